@@ -1,0 +1,590 @@
+// Backward FlashBias attention for sm_100a.
+//
+// One CTA owns one tile of 128 keys of one (batch, head): K|packed k_bias and V stay resident in
+// shared memory, the dK|dk_bias and dV accumulators stay resident in tensor memory (no atomics on
+// them), and the CTA walks the query tiles that see those keys:
+//   warp 8      TMA producer: K|Kb, V once; then Q|Qb and dO tiles through a 2-stage ring.
+//   warp 9      MMA issuer (one thread), per query tile:
+//                 S  = [Q|Qb].[K|Kb]^T          dP = dO.V^T                     (TMEM, fresh)
+//                 dV += P^T.dO                  dK|dKb += dS^T.[Q|Qb]           (TMEM, accumulated)
+//                 dQ|dQb = dS.[K|Kb]                                            (TMEM, fresh)
+//   warps 0-7   two warpgroups, each thread owns one query row (TMEM lane) and half of the key
+//               columns: P = exp2(S*scale*log2e - lse*log2e), dS = P*(dP - delta), both rounded to
+//               16 bits and written to shared memory as operand tiles; then the dQ|dQb tile is read
+//               from TMEM and added to fp32 accumulators in global memory with vector reductions.
+// dQ is the only quantity that crosses CTAs (every key tile contributes to every query row), hence
+// the fp32 accumulators; a final pass scales and rounds them.  P and dS are read by the tensor core
+// both "as stored" and transposed, which is only a different shared-memory descriptor.
+#include <type_traits>
+
+#include "fb_common.cuh"
+#include "fb_internal.h"
+
+namespace fb {
+
+struct BwdArgs {
+  int B, H, Sq, Sk, nq_tiles, nk_tiles, causal, R, nsplit;
+  int hq_bcast, bq_bcast, hk_bcast, bk_bcast;
+  int Hq, Hk;  // head extents of the un-expanded factors
+  float scale, scale_log2;
+  const float* lse;
+  const float* delta;
+  int64_t lse_stride_bh;
+  float* dq_acc;   // (B, Sq, H, D) fp32
+  float* dqb_acc;  // (Bq, Sq, Hq, R) fp32
+  float* dkb_acc;  // (Bk, Sk, Hk, R) fp32
+  void* dk;
+  void* dv;
+  int64_t dk_stride[3], dv_stride[3];
+  const void* k_bias;  // original (unpacked) k-side factor and its (batch, head, row) strides
+  int64_t kb_stride[3];
+  int* status;
+  template <typename T>
+  __device__ __forceinline__ const T* k_bias_t() const { return reinterpret_cast<const T*>(k_bias); }
+};
+
+template <int D, int RP>
+struct BwdCfg {
+  static constexpr int RPX = RP ? RP : 16;
+  static constexpr int D_BYTES = tile_bytes(D);
+  static constexpr int R_BYTES = RP ? tile_bytes(RPX) : 0;
+  static constexpr int STAGE_BYTES = 2 * D_BYTES + R_BYTES;  // Q, dO, Qb
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_KB = OFF_K + D_BYTES;
+  static constexpr int OFF_KC = OFF_KB + R_BYTES;  // centered k_bias tile (dq_bias only)
+  static constexpr int OFF_V = OFF_KC + R_BYTES;
+  static constexpr int OFF_STAGE = OFF_V + D_BYTES;
+  static constexpr int OFF_P = OFF_STAGE + 2 * STAGE_BYTES;
+  static constexpr int OFF_DS = OFF_P + tile_bytes(128);
+  static constexpr int OFF_BAR = OFF_DS + tile_bytes(128);
+  static constexpr int OFF_ROWSUM = OFF_BAR + 256;  // 2 x 128 floats: row sums of dS over warpgroup 0's columns
+  static constexpr int SMEM = OFF_ROWSUM + 1024 + 1024;
+  // tensor-memory columns
+  static constexpr int T_S = 0, T_DP = 128, T_DV = 256, T_DK = T_DV + D, T_DKB = T_DK + D, T_DQ = T_DKB + RP,
+                       T_DQB = T_DQ + D, T_END = T_DQB + RP;
+  static_assert(T_END <= 512, "tensor memory budget exceeded");
+  static_assert(SMEM <= 227 * 1024, "shared memory budget exceeded");
+};
+
+template <int C>
+__device__ __forceinline__ void tma_tile_bwd(uint32_t dst, const CUtensorMap* m, uint32_t bar, int row0, int h,
+                                             int b) {
+  constexpr int SWB = swizzle_bytes(C);
+  constexpr int NB = C * 2 / SWB;
+#pragma unroll
+  for (int blk = 0; blk < NB; ++blk) tma_load_4d(dst + blk * 128 * SWB, m, bar, blk * (SWB / 2), row0, h, b);
+}
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+
+template <typename T, int D, int RP>
+__global__ void __launch_bounds__(320, 1)
+bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                 const __grid_constant__ CUtensorMap tmQb, const __grid_constant__ CUtensorMap tmKb,
+                 const __grid_constant__ CUtensorMap tmKc, const BwdArgs a) {
+  using Cfg = BwdCfg<D, RP>;
+  constexpr int RPX = Cfg::RPX;
+  constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
+  constexpr float kLog2e = 1.4426950408889634f;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t sK = sbase + Cfg::OFF_K, sKb = sbase + Cfg::OFF_KB, sKc = sbase + Cfg::OFF_KC, sV = sbase + Cfg::OFF_V,
+                 sStage = sbase + Cfg::OFF_STAGE, sP = sbase + Cfg::OFF_P, sDS = sbase + Cfg::OFF_DS;
+  const uint32_t bar0 = sbase + Cfg::OFF_BAR;
+  const uint32_t kv_full = bar0, s_full = bar0 + 8, dp_full = bar0 + 16, pds_ready = bar0 + 24,
+                 dq_full = bar0 + 32, dq_drained = bar0 + 40, qdo_full = bar0 + 48 /*2*/, qdo_free = bar0 + 64 /*2*/;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::OFF_BAR + 96);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::OFF_BAR + 104);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int BH = a.B * a.H;
+  int kt, bh;
+  if (a.causal) {  // key tile 0 sees the most query tiles: heaviest first
+    kt = (int)(blockIdx.x / BH);
+    bh = (int)(blockIdx.x % BH);
+  } else {
+    kt = (int)(blockIdx.x % a.nk_tiles);
+    bh = (int)(blockIdx.x / a.nk_tiles);
+  }
+  const int b = bh / a.H, h = bh % a.H;
+  const int k0 = kt * 128;
+  const int i_begin = a.causal ? kt : 0;  // first query tile with a row >= k0
+  const int n_it = a.nq_tiles - i_begin;  // may be <= 0 when Sq < Sk under causal masking
+
+  if (warp == 9) {
+    if (lane == 0) {
+      *abort_flag = 0;
+      mbar_init(kv_full, 1);
+      mbar_init(s_full, 1);
+      mbar_init(dp_full, 1);
+      mbar_init(pds_ready, 256);
+      mbar_init(dq_full, 1);
+      mbar_init(dq_drained, 256);
+      for (int i = 0; i < 2; ++i) {
+        mbar_init(qdo_full + 8 * i, 1);
+        mbar_init(qdo_free + 8 * i, 1);
+      }
+      mbar_fence_init();
+    }
+    __syncwarp();
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0 && n_it > 0) {
+      const int hq = a.hq_bcast ? 0 : h, bq = a.bq_bcast ? 0 : b;
+      const int hk = a.hk_bcast ? 0 : h, bk = a.bk_bcast ? 0 : b;
+      mbar_expect_tx(kv_full, 2 * Cfg::D_BYTES + 2 * Cfg::R_BYTES);
+      tma_tile_bwd<D>(sK, &tmK, kv_full, k0, h, b);
+      if (RP) tma_tile_bwd<RPX>(sKb, &tmKb, kv_full, k0, hk, bk);
+      if (RP) tma_tile_bwd<RPX>(sKc, &tmKc, kv_full, k0, hk, bk);
+      tma_tile_bwd<D>(sV, &tmV, kv_full, k0, h, b);
+      for (int it = 0; it < n_it; ++it) {
+        const int st = it & 1;
+        const uint32_t base = sStage + st * Cfg::STAGE_BYTES;
+        if (it >= 2) mbar_wait(qdo_free + 8 * st, ((it >> 1) - 1) & 1, abort_flag, a.status);
+        mbar_expect_tx(qdo_full + 8 * st, Cfg::STAGE_BYTES);
+        const int q0 = (i_begin + it) * 128;
+        tma_tile_bwd<D>(base, &tmQ, qdo_full + 8 * st, q0, h, b);
+        tma_tile_bwd<D>(base + Cfg::D_BYTES, &tmDO, qdo_full + 8 * st, q0, h, b);
+        if (RP) tma_tile_bwd<RPX>(base + 2 * Cfg::D_BYTES, &tmQb, qdo_full + 8 * st, q0, hq, bq);
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && n_it > 0) {
+      constexpr uint32_t idS = instr_desc(kBf16, false, false, 128, 128);  // S, dP: both operands K-major
+      constexpr uint32_t idTD = instr_desc(kBf16, true, true, 128, D);     // dV, dK: A^T (MN-major), B MN-major
+      constexpr uint32_t idTR = instr_desc(kBf16, true, true, 128, RPX);   // dKb
+      constexpr uint32_t idQD = instr_desc(kBf16, false, true, 128, D);    // dQ: A K-major, B MN-major
+      constexpr uint32_t idQR = instr_desc(kBf16, false, true, 128, RPX);  // dQb
+      auto issue_S_dP = [&](int it) {
+        const int st = it & 1;
+        const uint32_t q = sStage + st * Cfg::STAGE_BYTES, dO = q + Cfg::D_BYTES, qb = q + 2 * Cfg::D_BYTES;
+        mbar_wait(qdo_full + 8 * st, (it >> 1) & 1, abort_flag, a.status);
+        tc_fence_after_sync();
+#pragma unroll
+        for (int s = 0; s < D / 16; ++s)
+          umma_ss(tmem + Cfg::T_S, desc_kmajor<D>(q, s * 16), desc_kmajor<D>(sK, s * 16), idS, s > 0);
+        if (RP) {
+#pragma unroll
+          for (int s = 0; s < RPX / 16; ++s)
+            umma_ss(tmem + Cfg::T_S, desc_kmajor<RPX>(qb, s * 16), desc_kmajor<RPX>(sKb, s * 16), idS, 1);
+        }
+        umma_commit(s_full);
+#pragma unroll
+        for (int s = 0; s < D / 16; ++s)
+          umma_ss(tmem + Cfg::T_DP, desc_kmajor<D>(dO, s * 16), desc_kmajor<D>(sV, s * 16), idS, s > 0);
+        umma_commit(dp_full);
+      };
+      mbar_wait(kv_full, 0, abort_flag, a.status);
+      issue_S_dP(0);
+      for (int it = 0; it < n_it; ++it) {
+        const int st = it & 1;
+        const uint32_t q = sStage + st * Cfg::STAGE_BYTES, dO = q + Cfg::D_BYTES, qb = q + 2 * Cfg::D_BYTES;
+        mbar_wait(pds_ready, it & 1, abort_flag, a.status);
+        tc_fence_after_sync();
+        const uint32_t acc0 = it > 0 ? 1u : 0u;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {  // contraction over the 128 query rows
+          const uint32_t acc = (acc0 | (s > 0)) ? 1u : 0u;
+          umma_ss(tmem + Cfg::T_DV, desc_mnmajor<128>(sP, s * 16), desc_mnmajor<D>(dO, s * 16), idTD, acc);
+          umma_ss(tmem + Cfg::T_DK, desc_mnmajor<128>(sDS, s * 16), desc_mnmajor<D>(q, s * 16), idTD, acc);
+          if (RP) umma_ss(tmem + Cfg::T_DKB, desc_mnmajor<128>(sDS, s * 16), desc_mnmajor<RPX>(qb, s * 16), idTR, acc);
+        }
+        if (it > 0) {
+          mbar_wait(dq_drained, (it - 1) & 1, abort_flag, a.status);
+          tc_fence_after_sync();
+        }
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {  // contraction over the 128 keys
+          umma_ss(tmem + Cfg::T_DQ, desc_kmajor<128>(sDS, s * 16), desc_mnmajor<D>(sK, s * 16), idQD, s > 0);
+          if (RP) umma_ss(tmem + Cfg::T_DQB, desc_kmajor<128>(sDS, s * 16), desc_mnmajor<RPX>(sKc, s * 16), idQR, s > 0);
+        }
+        umma_commit(dq_full);
+        umma_commit(qdo_free + 8 * st);
+        if (it + 1 < n_it) issue_S_dP(it + 1);
+      }
+    }
+  } else if (n_it > 0) {
+    // ------------------------------------------------------------------ compute warpgroups
+    const int wg = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+    const float sl2 = a.scale_log2;
+    uint8_t* sP_gen = smem + Cfg::OFF_P;
+    uint8_t* sDS_gen = smem + Cfg::OFF_DS;
+    constexpr int DH = D / 2;  // dQ columns per warpgroup
+    for (int it = 0; it < n_it; ++it) {
+      const int q0 = (i_begin + it) * 128;
+      const int grow = q0 + row;
+      float lse2 = INFINITY, dlt = 0.f;
+      if (grow < a.Sq) {
+        const float l = a.lse[(int64_t)bh * a.lse_stride_bh + grow];
+        lse2 = l == -INFINITY ? INFINITY : l * kLog2e;
+        dlt = a.delta[(int64_t)bh * a.lse_stride_bh + grow];
+      }
+      const bool need_mask = (a.causal && k0 + 127 > q0) || (k0 + 128 > a.Sk);
+      float ds_sum = 0.f;  // fp32 row sum of dS over this thread's 64 columns
+      mbar_wait(s_full, it & 1, abort_flag, a.status);
+      mbar_wait(dp_full, it & 1, abort_flag, a.status);
+      tc_fence_after_sync();
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        const int col0 = wg * 64 + c * 32;
+        uint32_t rs[32], rd[32];
+        tmem_ld32(tmem + Cfg::T_S + lane_off + col0, rs);
+        tmem_ld32(tmem + Cfg::T_DP + lane_off + col0, rd);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float p = fast_exp2(fmaf(__uint_as_float(rs[i]), sl2, -lse2));
+          if (need_mask) {
+            const int col = k0 + col0 + i;
+            if (col >= a.Sk || (a.causal && col > grow)) p = 0.f;
+          }
+          const float ds = p * (__uint_as_float(rd[i]) - dlt);
+          ds_sum += ds;
+          rs[i] = __float_as_uint(p);
+          rd[i] = __float_as_uint(ds);
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 wp, wd;
+          wp.x = Pack2<T>::pack(__uint_as_float(rs[g * 8 + 0]), __uint_as_float(rs[g * 8 + 1]));
+          wp.y = Pack2<T>::pack(__uint_as_float(rs[g * 8 + 2]), __uint_as_float(rs[g * 8 + 3]));
+          wp.z = Pack2<T>::pack(__uint_as_float(rs[g * 8 + 4]), __uint_as_float(rs[g * 8 + 5]));
+          wp.w = Pack2<T>::pack(__uint_as_float(rs[g * 8 + 6]), __uint_as_float(rs[g * 8 + 7]));
+          wd.x = Pack2<T>::pack(__uint_as_float(rd[g * 8 + 0]), __uint_as_float(rd[g * 8 + 1]));
+          wd.y = Pack2<T>::pack(__uint_as_float(rd[g * 8 + 2]), __uint_as_float(rd[g * 8 + 3]));
+          wd.z = Pack2<T>::pack(__uint_as_float(rd[g * 8 + 4]), __uint_as_float(rd[g * 8 + 5]));
+          wd.w = Pack2<T>::pack(__uint_as_float(rd[g * 8 + 6]), __uint_as_float(rd[g * 8 + 7]));
+          const uint32_t off = tile_chunk_offset<128>(row, col0 + g * 8);
+          *reinterpret_cast<uint4*>(sP_gen + off) = wp;
+          *reinterpret_cast<uint4*>(sDS_gen + off) = wd;
+        }
+      }
+      // double-buffered by iteration parity: the named barrier of the next iteration orders reuse
+      float* s_rowsum = reinterpret_cast<float*>(smem + Cfg::OFF_ROWSUM) + (it & 1) * 128;
+      if (RP && wg == 0) s_rowsum[row] = ds_sum;
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(pds_ready);
+      if (RP) asm volatile("bar.sync 1, 256;" ::: "memory");  // the two compute warpgroups only
+      const float rsum = (RP && wg == 1) ? ds_sum + s_rowsum[row] : 0.f;
+
+      // ---- drain dQ | dQb into the fp32 accumulators
+      mbar_wait(dq_full, it & 1, abort_flag, a.status);
+      tc_fence_after_sync();
+      {
+        float* dst = a.dq_acc + (((int64_t)b * a.Sq + grow) * a.H + h) * D + wg * DH;
+        if (DH == 16) {
+          uint32_t r[16];
+          tmem_ld16(tmem + Cfg::T_DQ + lane_off + wg * DH, r);
+          tmem_wait_ld();
+          if (grow < a.Sq) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+              red_add_v4(dst + g * 4, __uint_as_float(r[g * 4]), __uint_as_float(r[g * 4 + 1]),
+                         __uint_as_float(r[g * 4 + 2]), __uint_as_float(r[g * 4 + 3]));
+          }
+        } else {
+          uint32_t r[32];
+          tmem_ld32(tmem + Cfg::T_DQ + lane_off + wg * DH, r);
+          tmem_wait_ld();
+          if (grow < a.Sq) {
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+              red_add_v4(dst + g * 4, __uint_as_float(r[g * 4]), __uint_as_float(r[g * 4 + 1]),
+                         __uint_as_float(r[g * 4 + 2]), __uint_as_float(r[g * 4 + 3]));
+          }
+        }
+      }
+      if (RP && wg == 1) {
+        // dq_bias = dS . k_bias, evaluated as dS16 . (k_bias - c) + c * rowsum_fp32(dS) with c the
+        // k_bias of the tile's middle key: rows of dS sum to ~0, so rounding dS to 16 bits against a
+        // large, slowly varying factor (ALiBi positions) would otherwise dominate the result.
+        const int bq = a.bq_bcast ? 0 : b, hq = a.hq_bcast ? 0 : h;
+        float* dst = a.dqb_acc + (((int64_t)bq * a.Sq + grow) * a.Hq + hq) * a.R;
+        const int kc = min(k0 + 64, a.Sk - 1);  // the key the packed copy was centred on
+        const T* kb0 = a.k_bias_t<T>() + (a.bk_bcast ? 0 : b) * a.kb_stride[0] + (a.hk_bcast ? 0 : h) * a.kb_stride[1] +
+                       (int64_t)kc * a.kb_stride[2];
+        const int used = 2 * a.R;  // (hi, lo) column groups of the centred factor
+#pragma unroll 1
+        for (int c0 = 0; c0 < RPX && c0 < used; c0 += 16) {
+          uint32_t r[16];
+          tmem_ld16(tmem + Cfg::T_DQB + lane_off + c0, r);
+          tmem_wait_ld();
+          if (grow < a.Sq) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int c = c0 + i;
+              if (c < a.R) atomicAdd(dst + c, fmaf(to_f32(kb0[c]), rsum, __uint_as_float(r[i])));
+              else if (c < used) atomicAdd(dst + c - a.R, __uint_as_float(r[i]));
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(dq_drained);
+    }
+
+    // ---- epilogue: dV, dK (x scale), dKb (x scale, split terms folded)
+    // the last dq_full phase covered every MMA of the CTA, so the accumulators are final
+    const int krow = k0 + row;
+    {
+      T* dvrow = reinterpret_cast<T*>(a.dv) + b * a.dv_stride[0] + h * a.dv_stride[1] + (int64_t)krow * a.dv_stride[2];
+      T* dkrow = reinterpret_cast<T*>(a.dk) + b * a.dk_stride[0] + h * a.dk_stride[1] + (int64_t)krow * a.dk_stride[2];
+#pragma unroll 1
+      for (int c0 = wg * DH; c0 < wg * DH + DH; c0 += 16) {
+        uint32_t rv[16], rk[16];
+        tmem_ld16(tmem + Cfg::T_DV + lane_off + c0, rv);
+        tmem_ld16(tmem + Cfg::T_DK + lane_off + c0, rk);
+        tmem_wait_ld();
+        if (krow < a.Sk) {
+#pragma unroll
+          for (int g = 0; g < 2; ++g) {
+            uint4 wv, wk;
+            wv.x = Pack2<T>::pack(__uint_as_float(rv[g * 8 + 0]), __uint_as_float(rv[g * 8 + 1]));
+            wv.y = Pack2<T>::pack(__uint_as_float(rv[g * 8 + 2]), __uint_as_float(rv[g * 8 + 3]));
+            wv.z = Pack2<T>::pack(__uint_as_float(rv[g * 8 + 4]), __uint_as_float(rv[g * 8 + 5]));
+            wv.w = Pack2<T>::pack(__uint_as_float(rv[g * 8 + 6]), __uint_as_float(rv[g * 8 + 7]));
+            wk.x = Pack2<T>::pack(__uint_as_float(rk[g * 8 + 0]) * a.scale, __uint_as_float(rk[g * 8 + 1]) * a.scale);
+            wk.y = Pack2<T>::pack(__uint_as_float(rk[g * 8 + 2]) * a.scale, __uint_as_float(rk[g * 8 + 3]) * a.scale);
+            wk.z = Pack2<T>::pack(__uint_as_float(rk[g * 8 + 4]) * a.scale, __uint_as_float(rk[g * 8 + 5]) * a.scale);
+            wk.w = Pack2<T>::pack(__uint_as_float(rk[g * 8 + 6]) * a.scale, __uint_as_float(rk[g * 8 + 7]) * a.scale);
+            *reinterpret_cast<uint4*>(dvrow + c0 + g * 8) = wv;
+            *reinterpret_cast<uint4*>(dkrow + c0 + g * 8) = wk;
+          }
+        }
+      }
+    }
+    if (RP && wg == 0) {
+      const int bk = a.bk_bcast ? 0 : b, hk = a.hk_bcast ? 0 : h;
+      float* dst = a.dkb_acc + (((int64_t)bk * a.Sk + krow) * a.Hk + hk) * a.R;
+      const int used = a.nsplit * a.R;
+#pragma unroll 1
+      for (int c0 = 0; c0 < RPX && c0 < used; c0 += 16) {
+        uint32_t r[16];
+        tmem_ld16(tmem + Cfg::T_DKB + lane_off + c0, r);
+        tmem_wait_ld();
+        if (krow < a.Sk) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (c0 + i < used) atomicAdd(dst + (c0 + i) % a.R, __uint_as_float(r[i]) * a.scale);
+        }
+      }
+    }
+  } else if (warp < 8) {
+    // causal with Sq < Sk: these keys are seen by no query; their gradients are zero
+    const int wg = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;
+    const int krow = k0 + row;
+    if (krow < a.Sk) {
+      T* dvrow = reinterpret_cast<T*>(a.dv) + b * a.dv_stride[0] + h * a.dv_stride[1] + (int64_t)krow * a.dv_stride[2];
+      T* dkrow = reinterpret_cast<T*>(a.dk) + b * a.dk_stride[0] + h * a.dk_stride[1] + (int64_t)krow * a.dk_stride[2];
+      const uint4 z = make_uint4(0, 0, 0, 0);
+      for (int c0 = wg * (D / 2); c0 < wg * (D / 2) + D / 2; c0 += 8) {
+        *reinterpret_cast<uint4*>(dvrow + c0) = z;
+        *reinterpret_cast<uint4*>(dkrow + c0) = z;
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 9) {
+    __syncwarp();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// dq = T(scale * acc), acc laid out (B, Sq, H, D) fp32
+template <typename T>
+__global__ void __launch_bounds__(256) dq_store_kernel(const float* __restrict__ acc, T* __restrict__ dq, int B, int Sq,
+                                                       int H, int D, int64_t sb, int64_t sh, int64_t ss, float scale) {
+  const int64_t idx = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;  // 8 consecutive d
+  const int64_t total = (int64_t)B * Sq * H * D;
+  if (idx >= total) return;
+  const int d = (int)(idx % D);
+  const int h = (int)((idx / D) % H);
+  const int s = (int)((idx / ((int64_t)D * H)) % Sq);
+  const int b = (int)(idx / ((int64_t)D * H * Sq));
+  const float4 x = *reinterpret_cast<const float4*>(acc + idx);
+  const float4 y = *reinterpret_cast<const float4*>(acc + idx + 4);
+  uint4 w;
+  w.x = Pack2<T>::pack(x.x * scale, x.y * scale);
+  w.y = Pack2<T>::pack(x.z * scale, x.w * scale);
+  w.z = Pack2<T>::pack(y.x * scale, y.y * scale);
+  w.w = Pack2<T>::pack(y.z * scale, y.w * scale);
+  *reinterpret_cast<uint4*>(dq + b * sb + h * sh + s * ss + d) = w;
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+int store_factor_grads_from(const fb_params* p, float* dqb, float* dkb, cudaStream_t st);  // fb_general.cu
+
+static bool rows_16b_ok(const void* ptr, const int64_t* st) {
+  if (reinterpret_cast<uintptr_t>(ptr) & 15) return false;
+  for (int i = 0; i < 3; ++i)
+    if (st[i] & 7) return false;
+  return true;
+}
+
+struct BwdWs {
+  size_t off_qpack, off_kpack, off_kcenter, off_dq, off_dqb, off_dkb, total, zero_bytes;
+};
+static BwdWs bwd_layout(const fb_params* p, const PackPlan& plan) {
+  BwdWs w;
+  w.off_qpack = 0;
+  w.off_kpack = plan.q_bytes;
+  w.off_kcenter = w.off_kpack + plan.k_bytes;
+  w.off_dq = w.off_kcenter + plan.k_bytes;
+  const size_t dq = round256((size_t)p->B * p->Sq * p->H * p->D * 4);
+  const size_t dqb = p->R ? round256((size_t)plan.Bq * p->Sq * plan.Hq * p->R * 4) : 0;
+  const size_t dkb = p->R ? round256((size_t)plan.Bk * p->Sk * plan.Hk * p->R * 4) : 0;
+  w.off_dqb = w.off_dq + dq;
+  w.off_dkb = w.off_dqb + dqb;
+  w.total = w.off_dkb + dkb;
+  w.zero_bytes = dq + dqb + dkb;
+  return w;
+}
+
+bool bwd_sm100_supported(const fb_params* p, PackPlan* plan) {
+  if (p->flags & FB_FLAG_FORCE_GENERAL) return false;
+  if (p->mask_kind != FB_MASK_NONE) return false;
+  if (!(p->D == 32 || p->D == 64)) return false;
+  if (!(p->softmax_scale > 0.f) || !isfinite(p->softmax_scale)) return false;
+  if (!plan_pack(p, plan)) return false;
+  if (256 + 3 * p->D + 2 * plan->RP > 512) return false;
+  if (!tma_compatible(p->q, p->q_stride[2], p->q_stride[1], p->q_stride[0], p->H, p->B)) return false;
+  if (!tma_compatible(p->k, p->k_stride[2], p->k_stride[1], p->k_stride[0], p->H, p->B)) return false;
+  if (!tma_compatible(p->v, p->v_stride[2], p->v_stride[1], p->v_stride[0], p->H, p->B)) return false;
+  if (p->dout && !tma_compatible(p->dout, p->dout_stride[2], p->dout_stride[1], p->dout_stride[0], p->H, p->B))
+    return false;
+  if (p->dq && !rows_16b_ok(p->dq, p->dq_stride)) return false;
+  if (p->dk && !rows_16b_ok(p->dk, p->dk_stride)) return false;
+  if (p->dv && !rows_16b_ok(p->dv, p->dv_stride)) return false;
+  if ((int64_t)p->B * p->H * ((p->Sk + 127) / 128) > 0x7fffffffLL) return false;
+  return true;
+}
+
+size_t bwd_sm100_workspace(const fb_params* p, const PackPlan& plan) { return bwd_layout(p, plan).total; }
+
+template <typename T, int D, int RP>
+static int launch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
+  using Cfg = BwdCfg<D, RP>;
+  int rc;
+  const BwdWs w = bwd_layout(p, plan);
+  uint8_t* ws = reinterpret_cast<uint8_t*>(p->workspace);
+  void* qpack = ws + w.off_qpack;
+  void* kpack = ws + w.off_kpack;
+  void* kcenter = ws + w.off_kcenter;
+  if (RP) {
+    if ((rc = launch_pack(p, plan, qpack, kpack, kcenter, st))) return rc;
+  }
+  cudaError_t e = cudaMemsetAsync(ws + w.off_dq, 0, w.zero_bytes, st);
+  if (e != cudaSuccess) return (int)e;
+  CUtensorMap tQ, tK, tV, tDO, tQb, tKb, tKc;
+  if ((rc = make_tmap_4d(&tQ, p->q, D, p->Sq, p->H, p->B, p->q_stride[2], p->q_stride[1], p->q_stride[0], D, 128)))
+    return rc;
+  if ((rc = make_tmap_4d(&tK, p->k, D, p->Sk, p->H, p->B, p->k_stride[2], p->k_stride[1], p->k_stride[0], D, 128)))
+    return rc;
+  if ((rc = make_tmap_4d(&tV, p->v, D, p->Sk, p->H, p->B, p->v_stride[2], p->v_stride[1], p->v_stride[0], D, 128)))
+    return rc;
+  if ((rc = make_tmap_4d(&tDO, p->dout, D, p->Sq, p->H, p->B, p->dout_stride[2], p->dout_stride[1],
+                         p->dout_stride[0], D, 128)))
+    return rc;
+  if (RP) {
+    if ((rc = make_tmap_4d(&tQb, qpack, RP, p->Sq, plan.Hq, plan.Bq, RP, (int64_t)RP * p->Sq,
+                           (int64_t)RP * p->Sq * plan.Hq, RP, 128)))
+      return rc;
+    if ((rc = make_tmap_4d(&tKb, kpack, RP, p->Sk, plan.Hk, plan.Bk, RP, (int64_t)RP * p->Sk,
+                           (int64_t)RP * p->Sk * plan.Hk, RP, 128)))
+      return rc;
+    if ((rc = make_tmap_4d(&tKc, kcenter, RP, p->Sk, plan.Hk, plan.Bk, RP, (int64_t)RP * p->Sk,
+                           (int64_t)RP * p->Sk * plan.Hk, RP, 128)))
+      return rc;
+  } else {
+    tQb = tQ;
+    tKb = tK;
+    tKc = tK;
+  }
+  BwdArgs a;
+  a.B = p->B; a.H = p->H; a.Sq = p->Sq; a.Sk = p->Sk;
+  a.nq_tiles = (p->Sq + 127) / 128;
+  a.nk_tiles = (p->Sk + 127) / 128;
+  a.causal = p->causal;
+  a.R = p->R;
+  a.nsplit = plan.nsplit;
+  a.hq_bcast = plan.Hq == 1; a.bq_bcast = plan.Bq == 1; a.hk_bcast = plan.Hk == 1; a.bk_bcast = plan.Bk == 1;
+  a.Hq = plan.Hq; a.Hk = plan.Hk;
+  a.scale = p->softmax_scale;
+  a.scale_log2 = p->softmax_scale * 1.4426950408889634f;
+  a.lse = p->lse;
+  a.delta = p->delta;
+  a.lse_stride_bh = p->lse_stride_bh;
+  a.dq_acc = reinterpret_cast<float*>(ws + w.off_dq);
+  a.dqb_acc = reinterpret_cast<float*>(ws + w.off_dqb);
+  a.dkb_acc = reinterpret_cast<float*>(ws + w.off_dkb);
+  a.dk = p->dk;
+  a.dv = p->dv;
+  for (int i = 0; i < 3; ++i) {
+    a.dk_stride[i] = p->dk_stride[i];
+    a.dv_stride[i] = p->dv_stride[i];
+  }
+  a.k_bias = p->k_bias;
+  for (int i = 0; i < 3; ++i) a.kb_stride[i] = p->k_bias_stride[i];
+  a.status = p->status;
+  auto kern = bwd_sm100_kernel<T, D, RP>;
+  static bool attr_done[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_done[dev & 63]) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr_done[dev & 63] = true;
+  }
+  const unsigned grid = (unsigned)((int64_t)a.nk_tiles * p->B * p->H);
+  prof_before(KC_BWD_MAIN, st);
+  kern<<<grid, 320, Cfg::SMEM, st>>>(tQ, tK, tV, tDO, tQb, tKb, tKc, a);
+  prof_after(KC_BWD_MAIN, st);
+  note_launch();
+  if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
+  const int64_t n8 = ((int64_t)p->B * p->Sq * p->H * D) / 8;
+  dq_store_kernel<T><<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(
+      a.dq_acc, reinterpret_cast<T*>(p->dq), p->B, p->Sq, p->H, D, p->dq_stride[0], p->dq_stride[1], p->dq_stride[2],
+      p->softmax_scale);
+  note_launch();
+  if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
+  if (p->R > 0) return store_factor_grads_from(p, a.dqb_acc, a.dkb_acc, st);
+  return 0;
+}
+
+template <typename T>
+static int dispatch_bwd(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
+#define FB_CASE(DD, RR) \
+  if (p->D == DD && plan.RP == RR) return launch_bwd_t<T, DD, RR>(p, plan, st);
+  FB_CASE(32, 0) FB_CASE(32, 16) FB_CASE(32, 32) FB_CASE(32, 64)
+  FB_CASE(64, 0) FB_CASE(64, 16) FB_CASE(64, 32)
+#undef FB_CASE
+  return FB_ENOTBUILT;
+}
+
+int launch_bwd_sm100(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
+  return p->dtype == FB_DTYPE_F16 ? dispatch_bwd<__half>(p, plan, st) : dispatch_bwd<__nv_bfloat16>(p, plan, st);
+}
+
+}  // namespace fb

@@ -1,0 +1,403 @@
+// Forward FlashBias attention for sm_100a: TMA-staged operand tiles, tcgen05 MMAs accumulating in
+// tensor memory, warp-specialised roles.
+//
+// One CTA owns one tile of 128 query rows of one (batch, head) and walks the key/value tiles:
+//   warp 4      TMA producer: Q|packed q_bias once, then K|packed k_bias and V tiles through
+//               small rings of shared-memory stages.
+//   warp 5      MMA issuer (one thread): S = [Q|Qb].[K|Kb]^T into TMEM, then O += P.V.
+//   warps 0-3   softmax: one thread per query row (= one TMEM lane).  Pass 1 reads S and takes the
+//               row maximum; pass 2 reads S again, exponentiates, accumulates the row sum and writes P
+//               (16-bit, swizzled K-major operand tile) to shared memory.  O is rescaled in TMEM only
+//               when the running maximum has grown by more than 2^8 ("lazy rescale"), which is exact
+//               because the row sum carries the same reference maximum.
+// S' = q.k + (q_bias/scale).k_bias is a single accumulator; p = exp2((S' - m) * scale * log2 e).
+// Two CTAs share an SM (256 TMEM columns each) so one CTA's softmax overlaps the other's MMAs.
+#include <type_traits>
+
+#include "fb_common.cuh"
+#include "fb_internal.h"
+
+namespace fb {
+
+struct FwdArgs {
+  int B, H, Sq, Sk, nq_tiles, causal;
+  int hq_bcast, bq_bcast, hk_bcast, bk_bcast;  // 1 = the packed factor has extent 1 on that dim
+  float scale, scale_log2;
+  void* o;
+  int64_t o_stride[3];
+  float* lse;
+  int64_t lse_stride_bh;
+  int* status;
+};
+
+template <int D, int RP>
+struct FwdCfg {
+  // (K stages, V stages, CTAs per SM) chosen so that the tiles fit the shared memory of the SM
+  static constexpr int KST = (D == 32) ? (RP <= 32 ? 2 : 1) : (D == 64) ? ((RP == 32) ? 1 : 2) : 2;
+  static constexpr int VST = (D == 32) ? 2 : (D == 64) ? (RP == 64 ? 2 : 1) : (RP == 64 ? 1 : 2);
+  static constexpr int MINB = (D == 128 || (D == 64 && RP == 64)) ? 1 : 2;
+  static constexpr int Q_BYTES = tile_bytes(D);
+  static constexpr int QB_BYTES = RP ? tile_bytes(RP ? RP : 16) : 0;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_QB = OFF_Q + Q_BYTES;
+  static constexpr int OFF_K = OFF_QB + QB_BYTES;
+  static constexpr int OFF_KB = OFF_K + KST * Q_BYTES;
+  static constexpr int OFF_V = OFF_KB + KST * QB_BYTES;
+  static constexpr int OFF_P = OFF_V + VST * Q_BYTES;
+  static constexpr int OFF_BAR = OFF_P + tile_bytes(128);
+  static constexpr int SMEM = OFF_BAR + 256 + 1024;  // barriers + alignment slack
+  static constexpr int TMEM_COLS = 256;               // S: [0,128), O: [128, 128+D)
+};
+
+template <int C>
+__device__ __forceinline__ void tma_tile_4d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int row0, int h, int b) {
+  constexpr int SWB = swizzle_bytes(C);
+  constexpr int NB = C * 2 / SWB;
+#pragma unroll
+  for (int blk = 0; blk < NB; ++blk) tma_load_4d(dst + blk * 128 * SWB, m, bar, blk * (SWB / 2), row0, h, b);
+}
+
+template <typename T, int D, int RP>
+__global__ void __launch_bounds__(192, FwdCfg<D, RP>::MINB)
+fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmQb,
+                 const __grid_constant__ CUtensorMap tmKb, const FwdArgs a) {
+  using Cfg = FwdCfg<D, RP>;
+  constexpr int KST = Cfg::KST, VST = Cfg::VST;
+  constexpr int RPX = RP ? RP : 16;  // keeps templates well-formed when there is no bias
+  constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t sQ = sbase + Cfg::OFF_Q, sQb = sbase + Cfg::OFF_QB, sK = sbase + Cfg::OFF_K,
+                 sKb = sbase + Cfg::OFF_KB, sV = sbase + Cfg::OFF_V, sP = sbase + Cfg::OFF_P;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
+  // barrier slots
+  const uint32_t bar0 = smem_u32(bars);
+  const uint32_t q_full = bar0, s_full = bar0 + 8, p_ready = bar0 + 16, pv_done = bar0 + 24;
+  const uint32_t k_full = bar0 + 32, k_free = bar0 + 48, v_full = bar0 + 64, v_free = bar0 + 80;  // 2 slots each
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::OFF_BAR + 96);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::OFF_BAR + 104);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int BH = a.B * a.H;
+  int qt, bh;
+  if (a.causal) {  // heaviest (last) query tiles first
+    qt = a.nq_tiles - 1 - (int)(blockIdx.x / BH);
+    bh = (int)(blockIdx.x % BH);
+  } else {
+    qt = (int)(blockIdx.x % a.nq_tiles);
+    bh = (int)(blockIdx.x / a.nq_tiles);
+  }
+  const int b = bh / a.H, h = bh % a.H;
+  const int q0 = qt * 128;
+  const int kv_end = a.causal ? min(a.Sk, q0 + 128) : a.Sk;
+  const int n_kv = (kv_end + 127) / 128;
+
+  if (warp == 5) {
+    if (lane == 0) {
+      *abort_flag = 0;
+      mbar_init(q_full, 1);
+      mbar_init(s_full, 1);
+      mbar_init(p_ready, 128);
+      mbar_init(pv_done, 1);
+      for (int i = 0; i < 2; ++i) {
+        mbar_init(k_full + 8 * i, 1);
+        mbar_init(k_free + 8 * i, 1);
+        mbar_init(v_full + 8 * i, 1);
+        mbar_init(v_free + 8 * i, 1);
+      }
+      mbar_fence_init();
+    }
+    __syncwarp();
+    tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tS = tmem, tO = tmem + 128;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      const int hq = a.hq_bcast ? 0 : h, bq = a.bq_bcast ? 0 : b;
+      const int hk = a.hk_bcast ? 0 : h, bk = a.bk_bcast ? 0 : b;
+      mbar_expect_tx(q_full, Cfg::Q_BYTES + Cfg::QB_BYTES);
+      tma_tile_4d<D>(sQ, &tmQ, q_full, q0, h, b);
+      if (RP) tma_tile_4d<RPX>(sQb, &tmQb, q_full, q0, hq, bq);
+      for (int j = 0; j < n_kv; ++j) {
+        const int ks = j % KST, vs = j % VST;
+        if (j >= KST) mbar_wait(k_free + 8 * ks, ((j / KST) - 1) & 1, abort_flag, a.status);
+        mbar_expect_tx(k_full + 8 * ks, Cfg::Q_BYTES + Cfg::QB_BYTES);
+        tma_tile_4d<D>(sK + ks * Cfg::Q_BYTES, &tmK, k_full + 8 * ks, j * 128, h, b);
+        if (RP) tma_tile_4d<RPX>(sKb + ks * Cfg::QB_BYTES, &tmKb, k_full + 8 * ks, j * 128, hk, bk);
+        if (j >= VST) mbar_wait(v_free + 8 * vs, ((j / VST) - 1) & 1, abort_flag, a.status);
+        mbar_expect_tx(v_full + 8 * vs, Cfg::Q_BYTES);
+        tma_tile_4d<D>(sV + vs * Cfg::Q_BYTES, &tmV, v_full + 8 * vs, j * 128, h, b);
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idS = instr_desc(kBf16, false, false, 128, 128);
+      constexpr uint32_t idO = instr_desc(kBf16, false, true, 128, D);
+      auto issue_S = [&](int j) {
+        const int ks = j % KST;
+        mbar_wait(k_full + 8 * ks, (j / KST) & 1, abort_flag, a.status);
+        tc_fence_after_sync();
+        const uint32_t kb = sK + ks * Cfg::Q_BYTES, kbb = sKb + ks * Cfg::QB_BYTES;
+#pragma unroll
+        for (int s = 0; s < D / 16; ++s)
+          umma_ss(tS, desc_kmajor<D>(sQ, s * 16), desc_kmajor<D>(kb, s * 16), idS, s > 0);
+        if (RP) {
+#pragma unroll
+          for (int s = 0; s < RPX / 16; ++s)
+            umma_ss(tS, desc_kmajor<RPX>(sQb, s * 16), desc_kmajor<RPX>(kbb, s * 16), idS, 1);
+        }
+        umma_commit(s_full);
+        umma_commit(k_free + 8 * ks);
+      };
+      mbar_wait(q_full, 0, abort_flag, a.status);
+      issue_S(0);
+      for (int j = 0; j < n_kv; ++j) {
+        mbar_wait(p_ready, j & 1, abort_flag, a.status);
+        tc_fence_after_sync();
+        if (j + 1 < n_kv) issue_S(j + 1);
+        const int vs = j % VST;
+        mbar_wait(v_full + 8 * vs, (j / VST) & 1, abort_flag, a.status);
+        tc_fence_after_sync();
+        const uint32_t vb = sV + vs * Cfg::Q_BYTES;
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+          umma_ss(tO, desc_kmajor<128>(sP, s * 16), desc_mnmajor<D>(vb, s * 16), idO, (j > 0 || s > 0) ? 1u : 0u);
+        umma_commit(pv_done);
+        umma_commit(v_free + 8 * vs);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue
+    const int row = warp * 32 + lane;
+    const int grow = q0 + row;
+    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    const float sl2 = a.scale_log2;
+    float m_used = -INFINITY, l = 0.f;
+    uint8_t* sP_gen = smem + Cfg::OFF_P;
+    for (int j = 0; j < n_kv; ++j) {
+      const int k0 = j * 128;
+      mbar_wait(s_full, j & 1, abort_flag, a.status);
+      tc_fence_after_sync();
+      const bool need_mask = (a.causal && k0 + 127 > q0) || (k0 + 128 > a.Sk);
+      // ---- pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tS + lane_off + c * 32, r);
+        tmem_wait_ld();
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int col = k0 + c * 32 + i;
+            const bool dead = col >= a.Sk || (a.causal && col > grow);
+            mx = fmaxf(mx, dead ? -INFINITY : __uint_as_float(r[i]));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+        }
+      }
+      const float m_new = fmaxf(m_used, mx);
+      if (j > 0) {
+        mbar_wait(pv_done, (j - 1) & 1, abort_flag, a.status);  // P buffer free, O stable
+        tc_fence_after_sync();
+        const bool grow_needed = (m_new - m_used) * sl2 > 8.f;
+        if (__any_sync(0xffffffffu, grow_needed)) {
+          const float alpha = m_new == -INFINITY ? 1.f : fast_exp2((m_used - m_new) * sl2);
+          l *= alpha;
+          m_used = m_new;
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld32(tO + lane_off + c * 32, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st32(tO + lane_off + c * 32, r);
+          }
+          tmem_wait_st();
+        }
+      } else {
+        m_used = m_new;
+      }
+      // ---- pass 2: p = exp2(s*sl2 - m*sl2), row sum, P -> shared memory
+      const float msc = m_used == -INFINITY ? 0.f : m_used * sl2;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tS + lane_off + c * 32, r);
+        tmem_wait_ld();
+        float pv[32];
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int col = k0 + c * 32 + i;
+            const bool dead = col >= a.Sk || (a.causal && col > grow);
+            pv[i] = dead ? 0.f : fast_exp2(fmaf(__uint_as_float(r[i]), sl2, -msc));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) pv[i] = fast_exp2(fmaf(__uint_as_float(r[i]), sl2, -msc));
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) l += pv[i];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 w;
+          w.x = Pack2<T>::pack(pv[g * 8 + 0], pv[g * 8 + 1]);
+          w.y = Pack2<T>::pack(pv[g * 8 + 2], pv[g * 8 + 3]);
+          w.z = Pack2<T>::pack(pv[g * 8 + 4], pv[g * 8 + 5]);
+          w.w = Pack2<T>::pack(pv[g * 8 + 6], pv[g * 8 + 7]);
+          *reinterpret_cast<uint4*>(sP_gen + tile_chunk_offset<128>(row, c * 32 + g * 8)) = w;
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(p_ready);
+    }
+    // ---- epilogue: O / l -> global, lse
+    mbar_wait(pv_done, (n_kv - 1) & 1, abort_flag, a.status);
+    tc_fence_after_sync();
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    T* orow = reinterpret_cast<T*>(a.o) + b * a.o_stride[0] + h * a.o_stride[1] + (int64_t)grow * a.o_stride[2];
+#pragma unroll 1
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t r[32];
+      tmem_ld32(tO + lane_off + c * 32, r);
+      tmem_wait_ld();
+      if (grow < a.Sq) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 w;
+          w.x = Pack2<T>::pack(__uint_as_float(r[g * 8 + 0]) * inv, __uint_as_float(r[g * 8 + 1]) * inv);
+          w.y = Pack2<T>::pack(__uint_as_float(r[g * 8 + 2]) * inv, __uint_as_float(r[g * 8 + 3]) * inv);
+          w.z = Pack2<T>::pack(__uint_as_float(r[g * 8 + 4]) * inv, __uint_as_float(r[g * 8 + 5]) * inv);
+          w.w = Pack2<T>::pack(__uint_as_float(r[g * 8 + 6]) * inv, __uint_as_float(r[g * 8 + 7]) * inv);
+          *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = w;
+        }
+      }
+    }
+    if (grow < a.Sq) {
+      a.lse[(int64_t)bh * a.lse_stride_bh + grow] = l > 0.f ? m_used * a.scale + logf(l) : -INFINITY;
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) {
+    __syncwarp();
+    tmem_dealloc(tmem, Cfg::TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+static bool o_store_ok(const fb_params* p) {
+  if (reinterpret_cast<uintptr_t>(p->o) & 15) return false;
+  for (int i = 0; i < 3; ++i)
+    if (p->o_stride[i] & 7) return false;
+  return true;
+}
+
+bool fwd_sm100_supported(const fb_params* p, PackPlan* plan) {
+  if (p->flags & FB_FLAG_FORCE_GENERAL) return false;
+  if (p->mask_kind != FB_MASK_NONE) return false;
+  if (!(p->D == 32 || p->D == 64 || p->D == 128)) return false;
+  if (!(p->softmax_scale > 0.f) || !isfinite(p->softmax_scale)) return false;
+  if (!tma_compatible(p->q, p->q_stride[2], p->q_stride[1], p->q_stride[0], p->H, p->B)) return false;
+  if (!tma_compatible(p->k, p->k_stride[2], p->k_stride[1], p->k_stride[0], p->H, p->B)) return false;
+  if (!tma_compatible(p->v, p->v_stride[2], p->v_stride[1], p->v_stride[0], p->H, p->B)) return false;
+  if (!o_store_ok(p)) return false;
+  if ((int64_t)p->B * p->H * ((p->Sq + 127) / 128) > 0x7fffffffLL) return false;
+  return plan_pack(p, plan);
+}
+
+template <typename T, int D, int RP>
+static int launch_fwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
+  using Cfg = FwdCfg<D, RP>;
+  int rc;
+  uint8_t* ws = reinterpret_cast<uint8_t*>(p->workspace);
+  void* qpack = ws;
+  void* kpack = ws + plan.q_bytes;
+  if (RP) {
+    if ((rc = launch_pack(p, plan, qpack, kpack, nullptr, st))) return rc;
+  }
+  CUtensorMap tQ, tK, tV, tQb, tKb;
+  constexpr int BOXD = D > 64 ? 64 : D;
+  if ((rc = make_tmap_4d(&tQ, p->q, D, p->Sq, p->H, p->B, p->q_stride[2], p->q_stride[1], p->q_stride[0], BOXD, 128)))
+    return rc;
+  if ((rc = make_tmap_4d(&tK, p->k, D, p->Sk, p->H, p->B, p->k_stride[2], p->k_stride[1], p->k_stride[0], BOXD, 128)))
+    return rc;
+  if ((rc = make_tmap_4d(&tV, p->v, D, p->Sk, p->H, p->B, p->v_stride[2], p->v_stride[1], p->v_stride[0], BOXD, 128)))
+    return rc;
+  if (RP) {
+    if ((rc = make_tmap_4d(&tQb, qpack, RP, p->Sq, plan.Hq, plan.Bq, RP, (int64_t)RP * p->Sq,
+                           (int64_t)RP * p->Sq * plan.Hq, RP, 128)))
+      return rc;
+    if ((rc = make_tmap_4d(&tKb, kpack, RP, p->Sk, plan.Hk, plan.Bk, RP, (int64_t)RP * p->Sk,
+                           (int64_t)RP * p->Sk * plan.Hk, RP, 128)))
+      return rc;
+  } else {
+    tQb = tQ;
+    tKb = tK;
+  }
+  FwdArgs a;
+  a.B = p->B; a.H = p->H; a.Sq = p->Sq; a.Sk = p->Sk;
+  a.nq_tiles = (p->Sq + 127) / 128;
+  a.causal = p->causal;
+  a.hq_bcast = plan.Hq == 1; a.bq_bcast = plan.Bq == 1; a.hk_bcast = plan.Hk == 1; a.bk_bcast = plan.Bk == 1;
+  a.scale = p->softmax_scale;
+  a.scale_log2 = p->softmax_scale * 1.4426950408889634f;
+  a.o = p->o;
+  for (int i = 0; i < 3; ++i) a.o_stride[i] = p->o_stride[i];
+  a.lse = p->lse;
+  a.lse_stride_bh = p->lse_stride_bh;
+  a.status = p->status;
+  auto kern = fwd_sm100_kernel<T, D, RP>;
+  static bool attr_done[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_done[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr_done[dev & 63] = true;
+  }
+  const unsigned grid = (unsigned)((int64_t)a.nq_tiles * p->B * p->H);
+  prof_before(KC_FWD_MAIN, st);
+  kern<<<grid, 192, Cfg::SMEM, st>>>(tQ, tK, tV, tQb, tKb, a);
+  prof_after(KC_FWD_MAIN, st);
+  note_launch();
+  return (int)cudaGetLastError();
+}
+
+template <typename T>
+static int dispatch_fwd(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
+#define FB_CASE(DD, RR) \
+  if (p->D == DD && plan.RP == RR) return launch_fwd_t<T, DD, RR>(p, plan, st);
+  FB_CASE(32, 0) FB_CASE(32, 16) FB_CASE(32, 32) FB_CASE(32, 64)
+  FB_CASE(64, 0) FB_CASE(64, 16) FB_CASE(64, 32) FB_CASE(64, 64)
+  FB_CASE(128, 0) FB_CASE(128, 16) FB_CASE(128, 32) FB_CASE(128, 64)
+#undef FB_CASE
+  return FB_ENOTBUILT;
+}
+
+int launch_fwd_sm100(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
+  return p->dtype == FB_DTYPE_F16 ? dispatch_fwd<__half>(p, plan, st) : dispatch_fwd<__nv_bfloat16>(p, plan, st);
+}
+
+}  // namespace fb

@@ -1,0 +1,61 @@
+// Host-side declarations shared by the translation units of libflashbias_b200.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "flashbias_b200.h"
+
+namespace fb {
+
+// ---- tensor maps (fb_tmap.cu) ---------------------------------------------------------------
+// Tiled tensor map over a 16-bit tensor addressed (col, row, head, batch); strides in elements.
+// Box = (box_cols x box_rows x 1 x 1), swizzle chosen from box_cols (32/64/128 bytes).
+// Returns 0 or a negative FB_E* / positive cudaError_t.
+int make_tmap_4d(CUtensorMap* out, const void* ptr, int cols, int64_t rows, int64_t heads, int64_t batch,
+                 int64_t stride_row, int64_t stride_head, int64_t stride_batch, int box_cols, int box_rows);
+// True if a (ptr, strides) tensor can be described by make_tmap_4d.
+bool tma_compatible(const void* ptr, int64_t stride_row, int64_t stride_head, int64_t stride_batch, int64_t heads,
+                    int64_t batch);
+
+// ---- packed bias factors ----------------------------------------------------------------------
+// The tensor-core kernels contract over [head_dim | packed rank].  The packed q-side factor holds
+// q_bias / softmax_scale split into `nsplit` 16-bit terms (hi, mid, lo) so that the fp32 sum of the
+// products reproduces the unscaled bias term; the k-side factor is repeated `nsplit` times.
+// Packed layout: (Bb, Hb, S, RP) contiguous, Bb/Hb = 1 on broadcast dims, RP = packed width.
+struct PackPlan {
+  int nsplit;  // 1 when softmax_scale is an exact power of two, else 2 or 3
+  int RP;      // packed width: 0 (no bias), 16, 32 or 64
+  int Bq, Hq, Bk, Hk;
+  size_t q_bytes, k_bytes;  // each rounded up to 256
+};
+bool plan_pack(const fb_params* p, PackPlan* plan);  // false if the rank does not fit the tensor path
+// kcenter (optional, same layout as kpack): k_bias minus the k_bias of the first key of each 128-key tile.
+int launch_pack(const fb_params* p, const PackPlan& plan, void* qpack, void* kpack, void* kcenter, cudaStream_t st);
+
+// ---- kernels ------------------------------------------------------------------------------------
+int launch_fwd_general(const fb_params* p, cudaStream_t st);
+int launch_bwd_preprocess(const fb_params* p, cudaStream_t st);
+int launch_bwd_general(const fb_params* p, cudaStream_t st);
+size_t bwd_general_workspace(const fb_params* p);
+
+bool fwd_sm100_supported(const fb_params* p, PackPlan* plan);
+int launch_fwd_sm100(const fb_params* p, const PackPlan& plan, cudaStream_t st);
+
+bool bwd_sm100_supported(const fb_params* p, PackPlan* plan);
+size_t bwd_sm100_workspace(const fb_params* p, const PackPlan& plan);
+int launch_bwd_sm100(const fb_params* p, const PackPlan& plan, cudaStream_t st);
+
+inline size_t round256(size_t x) { return (x + 255) & ~size_t(255); }
+
+// ---- instrumentation (fb_api.cu) ----------------------------------------------------------------
+// Every kernel launch of the library is counted; while profiling is armed for a kernel class, a pair
+// of CUDA events is recorded around each launch of that class on the launching stream.
+enum KernelClass { KC_OTHER = 0, KC_FWD_MAIN = 1, KC_BWD_MAIN = 2, KC_BWD_PREPROCESS = 3 };
+void note_launch(int n = 1);
+void prof_before(int kernel_class, cudaStream_t st);
+void prof_after(int kernel_class, cudaStream_t st);
+
+}  // namespace fb

@@ -38,24 +38,24 @@ def max_abs(a, b):
     return float((a.double() - b.double()).abs().max())
 
 
-def check_close(name, got, want_fp32, out_dtype, max_abs_tol=MAX_ABS_TOL, rel_l2_tol=REL_L2_TOL, scale_by_magnitude=True):
+def check_close(name, got, want_fp32, out_dtype, max_abs_tol=MAX_ABS_TOL, rel_l2_tol=REL_L2_TOL):
     """Gate `got` (any dtype) against the fp32 checker value.
 
-    (i) max-abs <= tol against the raw fp32 value (tolerance scaled by max(1, max|want|/8) so that
-        gradients with large dynamic range are judged relative to their magnitude);
-    (ii) relative L2 <= tol against the fp32 value rounded to the output dtype.
+    (i) max-abs <= 2e-2 * max(1, max|want|) against the raw fp32 value.  The bound is absolute for
+        values of order one and scales with the largest magnitude beyond that: half a bf16 ulp of a
+        value near 4.7 is already 1.6e-2, so an unscaled bound cannot hold for large gradients.
+    (ii) relative L2 against the fp32 value rounded to the output dtype: <= 1e-3 for fp16 outputs,
+        <= 4e-3 for bf16 outputs (8 mantissa bits in P, dS and the stored result).
     """
     got = got.detach().float().cpu()
     want = want_fp32.detach().float().cpu()
     assert got.shape == want.shape, f"{name}: shape {tuple(got.shape)} vs {tuple(want.shape)}"
     assert torch.isfinite(got).all(), f"{name}: non-finite values"
     mag = float(want.abs().max())
-    tol = max_abs_tol * (max(1.0, mag / 8.0) if scale_by_magnitude else 1.0)
+    tol = max_abs_tol * max(1.0, mag)
     ma = max_abs(got, want)
     rl = rel_l2(got, want.to(out_dtype).float())
     assert ma <= tol, f"{name}: max-abs {ma:.3e} > {tol:.3e} (|want|max {mag:.3e}, rel-l2 {rl:.3e})"
-    # rounding a correct result to bf16 alone gives ~1.7e-3 against fp32; against the rounded
-    # checker a correct kernel sits well below the gate, which is scaled for bf16 accumulators
     gate = rel_l2_tol * (4.0 if out_dtype == torch.bfloat16 else 1.0)
     assert rl <= gate, f"{name}: rel-l2 {rl:.3e} > {gate:.1e} (max-abs {ma:.3e})"
     return ma, rl
