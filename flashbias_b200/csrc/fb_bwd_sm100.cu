@@ -46,19 +46,24 @@ struct BwdArgs {
 template <int D, int RP>
 struct BwdCfg {
   static constexpr int RPX = RP ? RP : 16;
+  // P and dS tiles are double-buffered when shared memory allows it, so that the exponentials of
+  // query tile i+1 overlap the dV/dK/dQ MMAs of query tile i.
+  static constexpr bool PIPE = (D == 32 && RP <= 32);
+  static constexpr int NBUF = PIPE ? 2 : 1;
   static constexpr int D_BYTES = tile_bytes(D);
   static constexpr int R_BYTES = RP ? tile_bytes(RPX) : 0;
   static constexpr int STAGE_BYTES = 2 * D_BYTES + R_BYTES;  // Q, dO, Qb
+  static constexpr int PDS_BYTES = 2 * tile_bytes(128);      // P then dS
   static constexpr int OFF_K = 0;
   static constexpr int OFF_KB = OFF_K + D_BYTES;
   static constexpr int OFF_KC = OFF_KB + R_BYTES;  // centered k_bias tile (dq_bias only)
   static constexpr int OFF_V = OFF_KC + R_BYTES;
   static constexpr int OFF_STAGE = OFF_V + D_BYTES;
-  static constexpr int OFF_P = OFF_STAGE + 2 * STAGE_BYTES;
-  static constexpr int OFF_DS = OFF_P + tile_bytes(128);
-  static constexpr int OFF_BAR = OFF_DS + tile_bytes(128);
-  static constexpr int OFF_ROWSUM = OFF_BAR + 256;  // 2 x 128 floats: row sums of dS over warpgroup 0's columns
-  static constexpr int SMEM = OFF_ROWSUM + 1024 + 1024;
+  static constexpr int OFF_PDS = OFF_STAGE + 2 * STAGE_BYTES;
+  static constexpr int OFF_BAR = OFF_PDS + NBUF * PDS_BYTES;
+  static constexpr int OFF_ROWSUM = OFF_BAR + 256;       // 2 x 2 x 128 floats: dS row sums of warpgroup 0
+  static constexpr int OFF_KBC = OFF_ROWSUM + 2048;      // 4 x RPX floats: k_bias of the 4 centre keys
+  static constexpr int SMEM = OFF_KBC + 4 * RPX * 4 + 1024;
   // tensor-memory columns
   static constexpr int T_S = 0, T_DP = 128, T_DV = 256, T_DK = T_DV + D, T_DKB = T_DK + D, T_DQ = T_DKB + RP,
                        T_DQB = T_DQ + D, T_END = T_DQB + RP;
@@ -95,7 +100,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
   const uint32_t sK = sbase + Cfg::OFF_K, sKb = sbase + Cfg::OFF_KB, sKc = sbase + Cfg::OFF_KC, sV = sbase + Cfg::OFF_V,
-                 sStage = sbase + Cfg::OFF_STAGE, sP = sbase + Cfg::OFF_P, sDS = sbase + Cfg::OFF_DS;
+                 sStage = sbase + Cfg::OFF_STAGE, sPDS = sbase + Cfg::OFF_PDS;
   const uint32_t bar0 = sbase + Cfg::OFF_BAR;
   const uint32_t kv_full = bar0, s_full = bar0 + 8, dp_full = bar0 + 16, pds_ready = bar0 + 24,
                  dq_full = bar0 + 32, dq_drained = bar0 + 40, qdo_full = bar0 + 48 /*2*/, qdo_free = bar0 + 64 /*2*/;
@@ -170,39 +175,55 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       constexpr uint32_t idTR = instr_desc(kBf16, true, true, 128, RPX);   // dKb
       constexpr uint32_t idQD = instr_desc(kBf16, false, true, 128, D);    // dQ: A K-major, B MN-major
       constexpr uint32_t idQR = instr_desc(kBf16, false, true, 128, RPX);  // dQb
+      // descriptor views built once (stage 0 / buffer 0); each MMA adds a constant to the address field
+      const DescBase kQ = kmajor_base<D>(sStage), kDO = kmajor_base<D>(sStage + Cfg::D_BYTES),
+                     kQb = kmajor_base<RPX>(sStage + 2 * Cfg::D_BYTES), kK = kmajor_base<D>(sK),
+                     kKb = kmajor_base<RPX>(sKb), kV = kmajor_base<D>(sV);
+      const DescBase mQ = mnmajor_base<D>(sStage), mDO = mnmajor_base<D>(sStage + Cfg::D_BYTES),
+                     mQb = mnmajor_base<RPX>(sStage + 2 * Cfg::D_BYTES), mK = mnmajor_base<D>(sK),
+                     mKc = mnmajor_base<RPX>(sKc), mP = mnmajor_base<128>(sPDS),
+                     mDS = mnmajor_base<128>(sPDS + tile_bytes(128)), kDS = kmajor_base<128>(sPDS + tile_bytes(128));
       auto issue_S_dP = [&](int it) {
         const int st = it & 1;
-        const uint32_t q = sStage + st * Cfg::STAGE_BYTES, dO = q + Cfg::D_BYTES, qb = q + 2 * Cfg::D_BYTES;
+        const uint32_t so = st * Cfg::STAGE_BYTES;
         mbar_wait(qdo_full + 8 * st, (it >> 1) & 1, abort_flag, a.status);
         tc_fence_after_sync();
 #pragma unroll
         for (int s = 0; s < D / 16; ++s)
-          umma_ss(tmem + Cfg::T_S, desc_kmajor<D>(q, s * 16), desc_kmajor<D>(sK, s * 16), idS, s > 0);
+          umma_ss(tmem + Cfg::T_S, desc_at(kQ, so + kmajor_step<D>(s)), desc_at(kK, kmajor_step<D>(s)), idS, s > 0);
         if (RP) {
 #pragma unroll
           for (int s = 0; s < RPX / 16; ++s)
-            umma_ss(tmem + Cfg::T_S, desc_kmajor<RPX>(qb, s * 16), desc_kmajor<RPX>(sKb, s * 16), idS, 1);
+            umma_ss(tmem + Cfg::T_S, desc_at(kQb, so + kmajor_step<RPX>(s)), desc_at(kKb, kmajor_step<RPX>(s)), idS, 1);
         }
         umma_commit(s_full);
 #pragma unroll
         for (int s = 0; s < D / 16; ++s)
-          umma_ss(tmem + Cfg::T_DP, desc_kmajor<D>(dO, s * 16), desc_kmajor<D>(sV, s * 16), idS, s > 0);
+          umma_ss(tmem + Cfg::T_DP, desc_at(kDO, so + kmajor_step<D>(s)), desc_at(kV, kmajor_step<D>(s)), idS, s > 0);
         umma_commit(dp_full);
       };
       mbar_wait(kv_full, 0, abort_flag, a.status);
       issue_S_dP(0);
       for (int it = 0; it < n_it; ++it) {
         const int st = it & 1;
-        const uint32_t q = sStage + st * Cfg::STAGE_BYTES, dO = q + Cfg::D_BYTES, qb = q + 2 * Cfg::D_BYTES;
+        const uint32_t so = st * Cfg::STAGE_BYTES;
+        const uint32_t po = (Cfg::PIPE ? st : 0) * Cfg::PDS_BYTES;
         mbar_wait(pds_ready, it & 1, abort_flag, a.status);
         tc_fence_after_sync();
+        // S and dP of the next query tile go first when P/dS are double-buffered: the compute warps then
+        // start on tile it+1 while the tensor core is still busy with dV/dK/dQ of tile it.
+        if (Cfg::PIPE && it + 1 < n_it) issue_S_dP(it + 1);
         const uint32_t acc0 = it > 0 ? 1u : 0u;
 #pragma unroll
         for (int s = 0; s < 8; ++s) {  // contraction over the 128 query rows
           const uint32_t acc = (acc0 | (s > 0)) ? 1u : 0u;
-          umma_ss(tmem + Cfg::T_DV, desc_mnmajor<128>(sP, s * 16), desc_mnmajor<D>(dO, s * 16), idTD, acc);
-          umma_ss(tmem + Cfg::T_DK, desc_mnmajor<128>(sDS, s * 16), desc_mnmajor<D>(q, s * 16), idTD, acc);
-          if (RP) umma_ss(tmem + Cfg::T_DKB, desc_mnmajor<128>(sDS, s * 16), desc_mnmajor<RPX>(qb, s * 16), idTR, acc);
+          umma_ss(tmem + Cfg::T_DV, desc_at(mP, po + mnmajor_step<128>(s)), desc_at(mDO, so + mnmajor_step<D>(s)),
+                  idTD, acc);
+          umma_ss(tmem + Cfg::T_DK, desc_at(mDS, po + mnmajor_step<128>(s)), desc_at(mQ, so + mnmajor_step<D>(s)),
+                  idTD, acc);
+          if (RP)
+            umma_ss(tmem + Cfg::T_DKB, desc_at(mDS, po + mnmajor_step<128>(s)),
+                    desc_at(mQb, so + mnmajor_step<RPX>(s)), idTR, acc);
         }
         if (it > 0) {
           mbar_wait(dq_drained, (it - 1) & 1, abort_flag, a.status);
@@ -210,12 +231,15 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
 #pragma unroll
         for (int s = 0; s < 8; ++s) {  // contraction over the 128 keys
-          umma_ss(tmem + Cfg::T_DQ, desc_kmajor<128>(sDS, s * 16), desc_mnmajor<D>(sK, s * 16), idQD, s > 0);
-          if (RP) umma_ss(tmem + Cfg::T_DQB, desc_kmajor<128>(sDS, s * 16), desc_mnmajor<RPX>(sKc, s * 16), idQR, s > 0);
+          umma_ss(tmem + Cfg::T_DQ, desc_at(kDS, po + kmajor_step<128>(s)), desc_at(mK, mnmajor_step<D>(s)), idQD,
+                  s > 0);
+          if (RP)
+            umma_ss(tmem + Cfg::T_DQB, desc_at(kDS, po + kmajor_step<128>(s)), desc_at(mKc, mnmajor_step<RPX>(s)),
+                    idQR, s > 0);
         }
         umma_commit(dq_full);
         umma_commit(qdo_free + 8 * st);
-        if (it + 1 < n_it) issue_S_dP(it + 1);
+        if (!Cfg::PIPE && it + 1 < n_it) issue_S_dP(it + 1);
       }
     }
   } else if (n_it > 0) {
@@ -224,42 +248,125 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     const float sl2 = a.scale_log2;
-    uint8_t* sP_gen = smem + Cfg::OFF_P;
-    uint8_t* sDS_gen = smem + Cfg::OFF_DS;
     constexpr int DH = D / 2;  // dQ columns per warpgroup
+    float* s_kbc = reinterpret_cast<float*>(smem + Cfg::OFF_KBC);
+    if (RP) {
+      // k_bias of the four keys the centred copy refers to (one per 32-key group), as fp32
+      const T* kb_bh = a.k_bias_t<T>() + (a.bk_bcast ? 0 : b) * a.kb_stride[0] + (a.hk_bcast ? 0 : h) * a.kb_stride[1];
+      for (int i = threadIdx.x; i < 4 * RPX; i += 256) {
+        const int g = i / RPX, c = i % RPX;
+        s_kbc[i] = c < a.R ? to_f32(kb_bh[(int64_t)min(k0 + 32 * g + 16, a.Sk - 1) * a.kb_stride[2] + c]) : 0.f;
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+    }
+
+    // Raw loads only: the values are consumed one iteration later, so the global-memory latency
+    // hides under the current tile's math instead of stalling the thread here.
+    auto load_row_stats = [&](int it, float& lse_raw, float& dlt) {
+      const int g = (i_begin + it) * 128 + row;
+      lse_raw = INFINITY;
+      dlt = 0.f;
+      if (it < n_it && g < a.Sq) {
+        lse_raw = __ldg(a.lse + (int64_t)bh * a.lse_stride_bh + g);
+        dlt = __ldg(a.delta + (int64_t)bh * a.lse_stride_bh + g);
+      }
+    };
+
+    // dQ | dQb of query tile `it` from TMEM into the fp32 accumulators in global memory
+    auto drain = [&](int it, const float (&rsum)[4]) {
+      const int grow = (i_begin + it) * 128 + row;
+      mbar_wait(dq_full, it & 1, abort_flag, a.status);
+      tc_fence_after_sync();
+      {
+        float* dst = a.dq_acc + (((int64_t)b * a.Sq + grow) * a.H + h) * D + wg * DH;
+        if (DH == 16) {
+          uint32_t r[16];
+          tmem_ld16(tmem + Cfg::T_DQ + lane_off + wg * DH, r);
+          tmem_wait_ld(r);
+          if (grow < a.Sq) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+              red_add_v4(dst + g * 4, __uint_as_float(r[g * 4]), __uint_as_float(r[g * 4 + 1]),
+                         __uint_as_float(r[g * 4 + 2]), __uint_as_float(r[g * 4 + 3]));
+          }
+        } else {
+          uint32_t r[32];
+          tmem_ld32(tmem + Cfg::T_DQ + lane_off + wg * DH, r);
+          tmem_wait_ld(r);
+          if (grow < a.Sq) {
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+              red_add_v4(dst + g * 4, __uint_as_float(r[g * 4]), __uint_as_float(r[g * 4 + 1]),
+                         __uint_as_float(r[g * 4 + 2]), __uint_as_float(r[g * 4 + 3]));
+          }
+        }
+      }
+      if (RP && wg == 1) {
+        // dq_bias = dS . k_bias, evaluated per group of 32 keys as dS16 . (k_bias - c) + c * rowsum_fp32(dS)
+        // with c the k_bias of the group's middle key: rows of dS sum to ~0, so rounding dS to 16 bits
+        // against a large, slowly varying factor (ALiBi positions) would otherwise dominate the result.
+        const int bq = a.bq_bcast ? 0 : b, hq = a.hq_bcast ? 0 : h;
+        float* dst = a.dqb_acc + (((int64_t)bq * a.Sq + grow) * a.Hq + hq) * a.R;
+        const int used = 2 * a.R;  // (hi, lo) column groups of the centred factor
+#pragma unroll 1
+        for (int c0 = 0; c0 < RPX && c0 < used; c0 += 16) {
+          uint32_t r[16];
+          tmem_ld16(tmem + Cfg::T_DQB + lane_off + c0, r);
+          tmem_wait_ld(r);
+          if (grow < a.Sq) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int c = c0 + i;
+              if (c < a.R) {
+                float v = __uint_as_float(r[i]);
+#pragma unroll
+                for (int g = 0; g < 4; ++g) v = fmaf(s_kbc[g * RPX + c], rsum[g], v);
+                atomicAdd(dst + c, v);
+              } else if (c < used) {
+                atomicAdd(dst + c - a.R, __uint_as_float(r[i]));
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(dq_drained);
+    };
+
+    float lse_raw, dlt;
+    load_row_stats(0, lse_raw, dlt);
+    float rsum_prev[4] = {0.f, 0.f, 0.f, 0.f};
     for (int it = 0; it < n_it; ++it) {
       const int q0 = (i_begin + it) * 128;
       const int grow = q0 + row;
-      float lse2 = INFINITY, dlt = 0.f;
-      if (grow < a.Sq) {
-        const float l = a.lse[(int64_t)bh * a.lse_stride_bh + grow];
-        lse2 = l == -INFINITY ? INFINITY : l * kLog2e;
-        dlt = a.delta[(int64_t)bh * a.lse_stride_bh + grow];
-      }
+      // a row that saw no key has lse = -inf: make its probabilities exactly zero
+      const float lse2_cur = lse_raw == -INFINITY ? INFINITY : lse_raw * kLog2e, dlt_cur = dlt;
+      load_row_stats(it + 1, lse_raw, dlt);  // next tile's statistics: the loads complete under this tile's math
+      if (!Cfg::PIPE && it > 0) drain(it - 1, rsum_prev);
+      uint8_t* sP_gen = smem + Cfg::OFF_PDS + (Cfg::PIPE ? (it & 1) : 0) * Cfg::PDS_BYTES;
+      uint8_t* sDS_gen = sP_gen + tile_bytes(128);
       const bool need_mask = (a.causal && k0 + 127 > q0) || (k0 + 128 > a.Sk);
-      float ds_sum = 0.f;  // fp32 row sum of dS over this thread's 64 columns
+      float ds_sum[2];  // fp32 row sums of dS over this thread's two 32-column groups
       mbar_wait(s_full, it & 1, abort_flag, a.status);
       mbar_wait(dp_full, it & 1, abort_flag, a.status);
       tc_fence_after_sync();
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
+      uint32_t rs0[32], rd0[32], rs1[32], rd1[32];
+      auto chunk = [&](uint32_t (&rs)[32], uint32_t (&rd)[32], int c) {
         const int col0 = wg * 64 + c * 32;
-        uint32_t rs[32], rd[32];
-        tmem_ld32(tmem + Cfg::T_S + lane_off + col0, rs);
-        tmem_ld32(tmem + Cfg::T_DP + lane_off + col0, rd);
-        tmem_wait_ld();
+        float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float p = fast_exp2(fmaf(__uint_as_float(rs[i]), sl2, -lse2));
+          float p = fast_exp2(fmaf(__uint_as_float(rs[i]), sl2, -lse2_cur));
           if (need_mask) {
             const int col = k0 + col0 + i;
             if (col >= a.Sk || (a.causal && col > grow)) p = 0.f;
           }
-          const float ds = p * (__uint_as_float(rd[i]) - dlt);
-          ds_sum += ds;
+          const float ds = p * (__uint_as_float(rd[i]) - dlt_cur);
+          if (i & 1) sum1 += ds; else sum0 += ds;
           rs[i] = __float_as_uint(p);
           rd[i] = __float_as_uint(ds);
         }
+        ds_sum[c] = sum0 + sum1;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           uint4 wp, wd;
@@ -275,71 +382,38 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           *reinterpret_cast<uint4*>(sP_gen + off) = wp;
           *reinterpret_cast<uint4*>(sDS_gen + off) = wd;
         }
-      }
+      };
+      const uint32_t tSl = tmem + Cfg::T_S + lane_off + wg * 64, tDl = tmem + Cfg::T_DP + lane_off + wg * 64;
+      tmem_ld32(tSl, rs0);
+      tmem_ld32(tDl, rd0);
+      tmem_wait_ld(rs0);
+      tmem_wait_ld(rd0);
+      tmem_ld32(tSl + 32, rs1);
+      tmem_ld32(tDl + 32, rd1);
+      chunk(rs0, rd0, 0);
+      tmem_wait_ld(rs1);
+      tmem_wait_ld(rd1);
+      chunk(rs1, rd1, 1);
       // double-buffered by iteration parity: the named barrier of the next iteration orders reuse
-      float* s_rowsum = reinterpret_cast<float*>(smem + Cfg::OFF_ROWSUM) + (it & 1) * 128;
-      if (RP && wg == 0) s_rowsum[row] = ds_sum;
+      float* s_rowsum = reinterpret_cast<float*>(smem + Cfg::OFF_ROWSUM) + (it & 1) * 256;
+      if (RP && wg == 0) {
+        s_rowsum[row] = ds_sum[0];
+        s_rowsum[128 + row] = ds_sum[1];
+      }
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(pds_ready);
       if (RP) asm volatile("bar.sync 1, 256;" ::: "memory");  // the two compute warpgroups only
-      const float rsum = (RP && wg == 1) ? ds_sum + s_rowsum[row] : 0.f;
-
-      // ---- drain dQ | dQb into the fp32 accumulators
-      mbar_wait(dq_full, it & 1, abort_flag, a.status);
-      tc_fence_after_sync();
-      {
-        float* dst = a.dq_acc + (((int64_t)b * a.Sq + grow) * a.H + h) * D + wg * DH;
-        if (DH == 16) {
-          uint32_t r[16];
-          tmem_ld16(tmem + Cfg::T_DQ + lane_off + wg * DH, r);
-          tmem_wait_ld();
-          if (grow < a.Sq) {
-#pragma unroll
-            for (int g = 0; g < 4; ++g)
-              red_add_v4(dst + g * 4, __uint_as_float(r[g * 4]), __uint_as_float(r[g * 4 + 1]),
-                         __uint_as_float(r[g * 4 + 2]), __uint_as_float(r[g * 4 + 3]));
-          }
-        } else {
-          uint32_t r[32];
-          tmem_ld32(tmem + Cfg::T_DQ + lane_off + wg * DH, r);
-          tmem_wait_ld();
-          if (grow < a.Sq) {
-#pragma unroll
-            for (int g = 0; g < 8; ++g)
-              red_add_v4(dst + g * 4, __uint_as_float(r[g * 4]), __uint_as_float(r[g * 4 + 1]),
-                         __uint_as_float(r[g * 4 + 2]), __uint_as_float(r[g * 4 + 3]));
-          }
-        }
-      }
+      float rsum[4] = {0.f, 0.f, ds_sum[0], ds_sum[1]};  // one per 32-key group of the tile
       if (RP && wg == 1) {
-        // dq_bias = dS . k_bias, evaluated as dS16 . (k_bias - c) + c * rowsum_fp32(dS) with c the
-        // k_bias of the tile's middle key: rows of dS sum to ~0, so rounding dS to 16 bits against a
-        // large, slowly varying factor (ALiBi positions) would otherwise dominate the result.
-        const int bq = a.bq_bcast ? 0 : b, hq = a.hq_bcast ? 0 : h;
-        float* dst = a.dqb_acc + (((int64_t)bq * a.Sq + grow) * a.Hq + hq) * a.R;
-        const int kc = min(k0 + 64, a.Sk - 1);  // the key the packed copy was centred on
-        const T* kb0 = a.k_bias_t<T>() + (a.bk_bcast ? 0 : b) * a.kb_stride[0] + (a.hk_bcast ? 0 : h) * a.kb_stride[1] +
-                       (int64_t)kc * a.kb_stride[2];
-        const int used = 2 * a.R;  // (hi, lo) column groups of the centred factor
-#pragma unroll 1
-        for (int c0 = 0; c0 < RPX && c0 < used; c0 += 16) {
-          uint32_t r[16];
-          tmem_ld16(tmem + Cfg::T_DQB + lane_off + c0, r);
-          tmem_wait_ld();
-          if (grow < a.Sq) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const int c = c0 + i;
-              if (c < a.R) atomicAdd(dst + c, fmaf(to_f32(kb0[c]), rsum, __uint_as_float(r[i])));
-              else if (c < used) atomicAdd(dst + c - a.R, __uint_as_float(r[i]));
-            }
-          }
-        }
+        rsum[0] = s_rowsum[row];
+        rsum[1] = s_rowsum[128 + row];
       }
-      tc_fence_before_sync();
-      mbar_arrive(dq_drained);
+      if (Cfg::PIPE && it > 0) drain(it - 1, rsum_prev);
+#pragma unroll
+      for (int g = 0; g < 4; ++g) rsum_prev[g] = rsum[g];
     }
+    drain(n_it - 1, rsum_prev);
 
     // ---- epilogue: dV, dK (x scale), dKb (x scale, split terms folded)
     // the last dq_full phase covered every MMA of the CTA, so the accumulators are final
@@ -352,7 +426,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         uint32_t rv[16], rk[16];
         tmem_ld16(tmem + Cfg::T_DV + lane_off + c0, rv);
         tmem_ld16(tmem + Cfg::T_DK + lane_off + c0, rk);
-        tmem_wait_ld();
+        tmem_wait_ld(rv);
+        tmem_wait_ld(rk);
         if (krow < a.Sk) {
 #pragma unroll
           for (int g = 0; g < 2; ++g) {
@@ -379,7 +454,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int c0 = 0; c0 < RPX && c0 < used; c0 += 16) {
         uint32_t r[16];
         tmem_ld16(tmem + Cfg::T_DKB + lane_off + c0, r);
-        tmem_wait_ld();
+        tmem_wait_ld(r);
         if (krow < a.Sk) {
 #pragma unroll
           for (int i = 0; i < 16; ++i)

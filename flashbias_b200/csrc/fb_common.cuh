@@ -170,6 +170,34 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t base, int row0, int co
   return smem_desc(addr, 128 * SWB, 8 * SWB, SWB);
 }
 
+// Descriptors whose base address is only known at run time: everything but the start-address field is
+// fixed per (tile width, major), so a view is built once and each MMA adds a compile-time byte offset.
+struct DescBase {
+  uint32_t lo, hi;
+};
+template <int C>
+__device__ __forceinline__ DescBase kmajor_base(uint32_t base) {
+  const uint64_t d = desc_kmajor<C>(base, 0);
+  return DescBase{(uint32_t)d, (uint32_t)(d >> 32)};
+}
+template <int C>
+__device__ __forceinline__ DescBase mnmajor_base(uint32_t base) {
+  const uint64_t d = desc_mnmajor<C>(base, 0, 0);
+  return DescBase{(uint32_t)d, (uint32_t)(d >> 32)};
+}
+// byte offset of K-step s (16 contraction elements) inside a [128][C] tile
+template <int C>
+__host__ __device__ constexpr uint32_t kmajor_step(int s) {
+  return ((s * 32) / swizzle_bytes(C)) * (128 * swizzle_bytes(C)) + (s * 32) % swizzle_bytes(C);
+}
+template <int C>
+__host__ __device__ constexpr uint32_t mnmajor_step(int s) {
+  return s * 16 * swizzle_bytes(C);
+}
+__device__ __forceinline__ uint64_t desc_at(DescBase d, uint32_t byte_off) {
+  return ((uint64_t)d.hi << 32) | (uint64_t)(d.lo + (byte_off >> 4));
+}
+
 // Instruction descriptor for tcgen05.mma.kind::f16: fp32 accumulate, A/B of the same 16-bit type.
 // c_format F32 at [4,6); a/b format (0 f16, 1 bf16) at [7,10)/[10,13); a/b major (1 = MN) at 15/16;
 // N>>3 at [17,23); M>>4 at [24,29).
@@ -231,6 +259,13 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
       : "memory");
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// The loaded registers are operands of the wait, so no use of them can be scheduled ahead of it.
+__device__ __forceinline__ void tmem_wait_ld(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31]) :: "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld(uint32_t (&r)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]) :: "memory");
+}
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------------------------

@@ -147,18 +147,21 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (lane == 0) {
       constexpr uint32_t idS = instr_desc(kBf16, false, false, 128, 128);
       constexpr uint32_t idO = instr_desc(kBf16, false, true, 128, D);
+      // descriptor views built once; each MMA only adds a constant to the start-address field
+      const DescBase dQ = kmajor_base<D>(sQ), dQb = kmajor_base<RPX>(sQb), dK = kmajor_base<D>(sK),
+                     dKb = kmajor_base<RPX>(sKb), dP = kmajor_base<128>(sP), dV = mnmajor_base<D>(sV);
       auto issue_S = [&](int j) {
         const int ks = j % KST;
         mbar_wait(k_full + 8 * ks, (j / KST) & 1, abort_flag, a.status);
         tc_fence_after_sync();
-        const uint32_t kb = sK + ks * Cfg::Q_BYTES, kbb = sKb + ks * Cfg::QB_BYTES;
+        const uint32_t ko = ks * Cfg::Q_BYTES, kbo = ks * Cfg::QB_BYTES;
 #pragma unroll
         for (int s = 0; s < D / 16; ++s)
-          umma_ss(tS, desc_kmajor<D>(sQ, s * 16), desc_kmajor<D>(kb, s * 16), idS, s > 0);
+          umma_ss(tS, desc_at(dQ, kmajor_step<D>(s)), desc_at(dK, ko + kmajor_step<D>(s)), idS, s > 0);
         if (RP) {
 #pragma unroll
           for (int s = 0; s < RPX / 16; ++s)
-            umma_ss(tS, desc_kmajor<RPX>(sQb, s * 16), desc_kmajor<RPX>(kbb, s * 16), idS, 1);
+            umma_ss(tS, desc_at(dQb, kmajor_step<RPX>(s)), desc_at(dKb, kbo + kmajor_step<RPX>(s)), idS, 1);
         }
         umma_commit(s_full);
         umma_commit(k_free + 8 * ks);
@@ -172,10 +175,11 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const int vs = j % VST;
         mbar_wait(v_full + 8 * vs, (j / VST) & 1, abort_flag, a.status);
         tc_fence_after_sync();
-        const uint32_t vb = sV + vs * Cfg::Q_BYTES;
+        const uint32_t vo = vs * Cfg::Q_BYTES;
 #pragma unroll
         for (int s = 0; s < 8; ++s)
-          umma_ss(tO, desc_kmajor<128>(sP, s * 16), desc_mnmajor<D>(vb, s * 16), idO, (j > 0 || s > 0) ? 1u : 0u);
+          umma_ss(tO, desc_at(dP, kmajor_step<128>(s)), desc_at(dV, vo + mnmajor_step<D>(s)), idO,
+                  (j > 0 || s > 0) ? 1u : 0u);
         umma_commit(pv_done);
         umma_commit(v_free + 8 * vs);
       }
@@ -188,31 +192,42 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const float sl2 = a.scale_log2;
     float m_used = -INFINITY, l = 0.f;
     uint8_t* sP_gen = smem + Cfg::OFF_P;
+    uint32_t ra[32], rb[32];  // two register buffers: the TMEM load of one chunk overlaps the math of the other
     for (int j = 0; j < n_kv; ++j) {
       const int k0 = j * 128;
       mbar_wait(s_full, j & 1, abort_flag, a.status);
       tc_fence_after_sync();
       const bool need_mask = (a.causal && k0 + 127 > q0) || (k0 + 128 > a.Sk);
-      // ---- pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tS + lane_off + c * 32, r);
-        tmem_wait_ld();
+      const uint32_t tSl = tS + lane_off;
+      // ---- pass 1: row maximum (four independent chains)
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      auto chunk_max = [&](const uint32_t (&r)[32], int c) {
         if (need_mask) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int col = k0 + c * 32 + i;
             const bool dead = col >= a.Sk || (a.causal && col > grow);
-            mx = fmaxf(mx, dead ? -INFINITY : __uint_as_float(r[i]));
+            mx4[i & 3] = fmaxf(mx4[i & 3], dead ? -INFINITY : __uint_as_float(r[i]));
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+          for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(r[i]));
         }
-      }
-      const float m_new = fmaxf(m_used, mx);
+      };
+      tmem_ld32(tSl, ra);
+      tmem_wait_ld(ra);
+      tmem_ld32(tSl + 32, rb);
+      chunk_max(ra, 0);
+      tmem_wait_ld(rb);
+      tmem_ld32(tSl + 64, ra);
+      chunk_max(rb, 1);
+      tmem_wait_ld(ra);
+      tmem_ld32(tSl + 96, rb);
+      chunk_max(ra, 2);
+      tmem_wait_ld(rb);
+      tmem_ld32(tSl, ra);  // first chunk of pass 2
+      chunk_max(rb, 3);
+      const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])));
       if (j > 0) {
         mbar_wait(pv_done, (j - 1) & 1, abort_flag, a.status);  // P buffer free, O stable
         tc_fence_after_sync();
@@ -223,12 +238,11 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           m_used = m_new;
 #pragma unroll 1
           for (int c = 0; c < D / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld32(tO + lane_off + c * 32, r);
-            tmem_wait_ld();
+            tmem_ld32(tO + lane_off + c * 32, rb);
+            tmem_wait_ld(rb);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st32(tO + lane_off + c * 32, r);
+            for (int i = 0; i < 32; ++i) rb[i] = __float_as_uint(__uint_as_float(rb[i]) * alpha);
+            tmem_st32(tO + lane_off + c * 32, rb);
           }
           tmem_wait_st();
         }
@@ -237,35 +251,47 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       // ---- pass 2: p = exp2(s*sl2 - m*sl2), row sum, P -> shared memory
       const float msc = m_used == -INFINITY ? 0.f : m_used * sl2;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tS + lane_off + c * 32, r);
-        tmem_wait_ld();
-        float pv[32];
+      float l4[4] = {0.f, 0.f, 0.f, 0.f};
+      auto chunk_exp = [&](uint32_t (&r)[32], int c) {
         if (need_mask) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int col = k0 + c * 32 + i;
             const bool dead = col >= a.Sk || (a.causal && col > grow);
-            pv[i] = dead ? 0.f : fast_exp2(fmaf(__uint_as_float(r[i]), sl2, -msc));
+            const float p = dead ? 0.f : fast_exp2(fmaf(__uint_as_float(r[i]), sl2, -msc));
+            l4[i & 3] += p;
+            r[i] = __float_as_uint(p);
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) pv[i] = fast_exp2(fmaf(__uint_as_float(r[i]), sl2, -msc));
+          for (int i = 0; i < 32; ++i) {
+            const float p = fast_exp2(fmaf(__uint_as_float(r[i]), sl2, -msc));
+            l4[i & 3] += p;
+            r[i] = __float_as_uint(p);
+          }
         }
-#pragma unroll
-        for (int i = 0; i < 32; ++i) l += pv[i];
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           uint4 w;
-          w.x = Pack2<T>::pack(pv[g * 8 + 0], pv[g * 8 + 1]);
-          w.y = Pack2<T>::pack(pv[g * 8 + 2], pv[g * 8 + 3]);
-          w.z = Pack2<T>::pack(pv[g * 8 + 4], pv[g * 8 + 5]);
-          w.w = Pack2<T>::pack(pv[g * 8 + 6], pv[g * 8 + 7]);
+          w.x = Pack2<T>::pack(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]));
+          w.y = Pack2<T>::pack(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]));
+          w.z = Pack2<T>::pack(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
+          w.w = Pack2<T>::pack(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
           *reinterpret_cast<uint4*>(sP_gen + tile_chunk_offset<128>(row, c * 32 + g * 8)) = w;
         }
-      }
+      };
+      tmem_wait_ld(ra);
+      tmem_ld32(tSl + 32, rb);
+      chunk_exp(ra, 0);
+      tmem_wait_ld(rb);
+      tmem_ld32(tSl + 64, ra);
+      chunk_exp(rb, 1);
+      tmem_wait_ld(ra);
+      tmem_ld32(tSl + 96, rb);
+      chunk_exp(ra, 2);
+      tmem_wait_ld(rb);
+      chunk_exp(rb, 3);
+      l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(p_ready);
@@ -279,7 +305,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     for (int c = 0; c < D / 32; ++c) {
       uint32_t r[32];
       tmem_ld32(tO + lane_off + c * 32, r);
-      tmem_wait_ld();
+      tmem_wait_ld(r);
       if (grow < a.Sq) {
 #pragma unroll
         for (int g = 0; g < 4; ++g) {

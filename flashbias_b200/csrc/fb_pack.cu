@@ -59,9 +59,9 @@ __global__ void __launch_bounds__(256) pack_factor_kernel(const T* __restrict__ 
   T* out = dst + idx * RP;
   for (int c = nsplit * R; c < RP; ++c) out[c] = from_f32<T>(0.f);
   if (dst_centered) {
-    // k-side factor minus the factor of the middle key of its 128-row tile: small-magnitude copy used
+    // k-side factor minus the factor of the middle key of its group of 32 keys: small-magnitude copy used
     // for dq_bias = dS.k_bias (the removed constant is re-applied in fp32 through the row sum of dS)
-    int s0 = (s & ~127) + 64;
+    int s0 = (s & ~31) + 16;
     if (s0 > S - 1) s0 = S - 1;
     const T* in0 = src + b * sb + h * sh + (int64_t)s0 * ss;
     T* outc = dst_centered + idx * RP;

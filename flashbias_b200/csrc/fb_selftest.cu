@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
   for (int c0 = 0; c0 < N; c0 += 16) {
     uint32_t r[16];
     tmem_ld16(taddr + c0, r);
-    tmem_wait_ld();
+    tmem_wait_ld(r);
 #pragma unroll
     for (int i = 0; i < 16; ++i) d_out[(size_t)tid * N + c0 + i] = __uint_as_float(r[i]);
   }
