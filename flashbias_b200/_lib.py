@@ -49,6 +49,8 @@ EXPORTS = {
     "fb_bwd_uses_tensor_path": (C.c_int, [C.POINTER(FbParams)]),
     "fb_fwd_workspace_bytes": (C.c_size_t, [C.POINTER(FbParams)]),
     "fb_fwd": (C.c_int, [C.POINTER(FbParams), C.c_void_p]),
+    "fb_fwd_noalloc": (C.c_int, [C.POINTER(FbParams), C.c_void_p]),
+    "fb_fwd_noalloc_capacity": (C.c_size_t, []),
     "fb_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(FbParams)]),
     "fb_bwd_preprocess": (C.c_int, [C.POINTER(FbParams), C.c_void_p]),
     "fb_bwd": (C.c_int, [C.POINTER(FbParams), C.c_void_p]),

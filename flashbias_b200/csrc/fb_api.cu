@@ -151,6 +151,7 @@ extern "C" const char* fb_strerror(int code) {
     case FB_EINVAL_LSE: return "lse_stride_bh is smaller than Sq";
     case FB_ENOTBUILT: return "kernel variant not available in this build";
     case FB_EDEVICE: return "a kernel reported a device-side error";
+    case FB_EINVAL_SIZE: return "problem needs more scratch than the fixed-capacity entry point holds";
     default: return code > 0 ? cudaGetErrorString(static_cast<cudaError_t>(code)) : "unknown flashbias error";
   }
 }

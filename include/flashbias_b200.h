@@ -52,6 +52,7 @@ extern "C" {
 #define FB_EINVAL_LSE -8       /* lse_stride_bh smaller than Sq */
 #define FB_ENOTBUILT -9        /* the library was built without the requested kernel */
 #define FB_EDEVICE -10         /* a kernel reported a device-side error through the status word */
+#define FB_EINVAL_SIZE -11     /* the problem needs more scratch than a fixed-capacity entry point holds */
 
 /*
  * One problem description, shared by forward and backward.
@@ -106,6 +107,31 @@ int fb_fwd(const fb_params *p, void *cuda_stream);
 size_t fb_bwd_workspace_bytes(const fb_params *p);
 int fb_bwd_preprocess(const fb_params *p, void *cuda_stream);
 int fb_bwd(const fb_params *p, void *cuda_stream);
+
+/*
+ * fb_fwd for callers that cannot allocate device memory.  This entry point has no counterpart in the
+ * reference, whose launcher allocates its scratch with torch.
+ *
+ * Who needs it: hosts that call the library from a hook which receives only input and output buffers
+ * and must not call cudaMalloc there -- for example the enqueue step of an inference-runtime plugin or a
+ * custom-op ABI without a workspace argument.  A device allocation inside such a call would synchronise
+ * the device and can fail under memory pressure in the middle of a step.
+ *
+ * Same arguments and results as fb_fwd; p->workspace and p->workspace_bytes are ignored.  The scratch
+ * (packed bias factors) lives in a fixed array of FB_NOALLOC_SCRATCH_BYTES inside the library, held by
+ * every GPU that loads the library until the process exits.  A problem whose fb_fwd_workspace_bytes()
+ * exceeds that capacity is rejected with FB_EINVAL_SIZE before anything is launched.  No cudaMalloc,
+ * cudaFree or other allocating call is made.
+ *
+ * The first call on each device looks up the device address of the array (cudaGetSymbolAddress, with
+ * that device current); make that first call outside any stream capture.  All calls on a device share
+ * the one array, which keeps the previous call's contents: every byte a call reads it has written
+ * itself first, so nothing needs clearing, but two calls that overlap on the GPU (different streams)
+ * race on it -- keep them on one stream or order them with events.
+ */
+#define FB_NOALLOC_SCRATCH_BYTES (32u << 20)
+size_t fb_fwd_noalloc_capacity(void);
+int fb_fwd_noalloc(const fb_params *p, void *cuda_stream);
 
 /*
  * Instrumentation (no counterpart in the reference).  fb_launch_count: kernels launched by this
