@@ -50,6 +50,8 @@ struct BwdCfg {
   // query tile i+1 overlap the dV/dK/dQ MMAs of query tile i.
   static constexpr bool PIPE = (D == 32 && RP <= 32);
   static constexpr int NBUF = PIPE ? 2 : 1;
+  // [Q|Qb] and [K|Kc] read as one MN-major operand of N = D + RP (two 64-byte-swizzled tiles)
+  static constexpr bool MERGE = (D == 32 && RP == 32);
   static constexpr int D_BYTES = tile_bytes(D);
   static constexpr int R_BYTES = RP ? tile_bytes(RPX) : 0;
   static constexpr int STAGE_BYTES = 2 * D_BYTES + R_BYTES;  // Q, dO, Qb
@@ -183,6 +185,12 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                      mQb = mnmajor_base<RPX>(sStage + 2 * Cfg::D_BYTES), mK = mnmajor_base<D>(sK),
                      mKc = mnmajor_base<RPX>(sKc), mP = mnmajor_base<128>(sPDS),
                      mDS = mnmajor_base<128>(sPDS + tile_bytes(128)), kDS = kmajor_base<128>(sPDS + tile_bytes(128));
+      // merged views: second 32-column block found at a leading-dimension offset of the tile distance
+      const uint64_t dQQb = smem_desc(sStage, 2 * Cfg::D_BYTES, 8 * 64, 64);
+      const uint64_t dKKc = smem_desc(sK, Cfg::OFF_KC - Cfg::OFF_K, 8 * 64, 64);
+      const DescBase mQQb{(uint32_t)dQQb, (uint32_t)(dQQb >> 32)}, mKKc{(uint32_t)dKKc, (uint32_t)(dKKc >> 32)};
+      constexpr uint32_t idTM = instr_desc(kBf16, true, true, 128, D + RPX);   // dK|dKb merged
+      constexpr uint32_t idQM = instr_desc(kBf16, false, true, 128, D + RPX);  // dQ|dQb merged
       auto issue_S_dP = [&](int it) {
         const int st = it & 1;
         const uint32_t so = st * Cfg::STAGE_BYTES;
@@ -219,11 +227,16 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           const uint32_t acc = (acc0 | (s > 0)) ? 1u : 0u;
           umma_ss(tmem + Cfg::T_DV, desc_at(mP, po + mnmajor_step<128>(s)), desc_at(mDO, so + mnmajor_step<D>(s)),
                   idTD, acc);
-          umma_ss(tmem + Cfg::T_DK, desc_at(mDS, po + mnmajor_step<128>(s)), desc_at(mQ, so + mnmajor_step<D>(s)),
-                  idTD, acc);
-          if (RP)
-            umma_ss(tmem + Cfg::T_DKB, desc_at(mDS, po + mnmajor_step<128>(s)),
-                    desc_at(mQb, so + mnmajor_step<RPX>(s)), idTR, acc);
+          if (Cfg::MERGE) {
+            umma_ss(tmem + Cfg::T_DK, desc_at(mDS, po + mnmajor_step<128>(s)),
+                    desc_at(mQQb, so + mnmajor_step<D>(s)), idTM, acc);
+          } else {
+            umma_ss(tmem + Cfg::T_DK, desc_at(mDS, po + mnmajor_step<128>(s)), desc_at(mQ, so + mnmajor_step<D>(s)),
+                    idTD, acc);
+            if (RP)
+              umma_ss(tmem + Cfg::T_DKB, desc_at(mDS, po + mnmajor_step<128>(s)),
+                      desc_at(mQb, so + mnmajor_step<RPX>(s)), idTR, acc);
+          }
         }
         if (it > 0) {
           mbar_wait(dq_drained, (it - 1) & 1, abort_flag, a.status);
@@ -231,11 +244,16 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
 #pragma unroll
         for (int s = 0; s < 8; ++s) {  // contraction over the 128 keys
-          umma_ss(tmem + Cfg::T_DQ, desc_at(kDS, po + kmajor_step<128>(s)), desc_at(mK, mnmajor_step<D>(s)), idQD,
-                  s > 0);
-          if (RP)
-            umma_ss(tmem + Cfg::T_DQB, desc_at(kDS, po + kmajor_step<128>(s)), desc_at(mKc, mnmajor_step<RPX>(s)),
-                    idQR, s > 0);
+          if (Cfg::MERGE) {
+            umma_ss(tmem + Cfg::T_DQ, desc_at(kDS, po + kmajor_step<128>(s)), desc_at(mKKc, mnmajor_step<D>(s)), idQM,
+                    s > 0);
+          } else {
+            umma_ss(tmem + Cfg::T_DQ, desc_at(kDS, po + kmajor_step<128>(s)), desc_at(mK, mnmajor_step<D>(s)), idQD,
+                    s > 0);
+            if (RP)
+              umma_ss(tmem + Cfg::T_DQB, desc_at(kDS, po + kmajor_step<128>(s)),
+                      desc_at(mKc, mnmajor_step<RPX>(s)), idQR, s > 0);
+          }
         }
         umma_commit(dq_full);
         umma_commit(qdo_free + 8 * st);
@@ -542,7 +560,9 @@ bool bwd_sm100_supported(const fb_params* p, PackPlan* plan) {
   if (p->mask_kind != FB_MASK_NONE) return false;
   if (!(p->D == 32 || p->D == 64)) return false;
   if (!(p->softmax_scale > 0.f) || !isfinite(p->softmax_scale)) return false;
-  if (!plan_pack(p, plan)) return false;
+  // head_dim 32: packed factors as wide as the head (32 columns), so that [Q|Qb] and [K|Kc] are pairs of
+  // equally laid-out tiles and dK|dk_bias, dQ|dq_bias are single MMAs of N = 64
+  if (!plan_pack(p, plan, p->D == 32 ? 32 : 16)) return false;
   if (256 + 3 * p->D + 2 * plan->RP > 512) return false;
   if (!tma_compatible(p->q, p->q_stride[2], p->q_stride[1], p->q_stride[0], p->H, p->B)) return false;
   if (!tma_compatible(p->k, p->k_stride[2], p->k_stride[1], p->k_stride[0], p->H, p->B)) return false;

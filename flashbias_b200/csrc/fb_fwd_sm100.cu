@@ -33,9 +33,9 @@ struct FwdArgs {
 template <int D, int RP>
 struct FwdCfg {
   // (K stages, V stages, CTAs per SM) chosen so that the tiles fit the shared memory of the SM
-  static constexpr int KST = (D == 32) ? (RP <= 32 ? 2 : 1) : (D == 64) ? ((RP == 32) ? 1 : 2) : 2;
-  static constexpr int VST = (D == 32) ? 2 : (D == 64) ? (RP == 64 ? 2 : 1) : (RP == 64 ? 1 : 2);
-  static constexpr int MINB = (D == 128 || (D == 64 && RP == 64)) ? 1 : 2;
+  static constexpr int KST = 2;
+  static constexpr int VST = 2;
+  static constexpr int MINB = (D == 128) ? 1 : 2;
   static constexpr int Q_BYTES = tile_bytes(D);
   static constexpr int QB_BYTES = RP ? tile_bytes(RP ? RP : 16) : 0;
   static constexpr int OFF_Q = 0;
@@ -43,10 +43,11 @@ struct FwdCfg {
   static constexpr int OFF_K = OFF_QB + QB_BYTES;
   static constexpr int OFF_KB = OFF_K + KST * Q_BYTES;
   static constexpr int OFF_V = OFF_KB + KST * QB_BYTES;
-  static constexpr int OFF_P = OFF_V + VST * Q_BYTES;
-  static constexpr int OFF_BAR = OFF_P + tile_bytes(128);
+  static constexpr int OFF_BAR = OFF_V + VST * Q_BYTES;
   static constexpr int SMEM = OFF_BAR + 256 + 1024;  // barriers + alignment slack
-  static constexpr int TMEM_COLS = 256;               // S: [0,128), O: [128, 128+D)
+  // tensor memory: S fp32 [0,128), P 16-bit pairs [128,192), O fp32 [192, 192+D)
+  static constexpr int T_S = 0, T_P = 128, T_O = 192;
+  static constexpr int TMEM_COLS = (T_O + D <= 256) ? 256 : 512;
 };
 
 template <int C>
@@ -71,7 +72,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
   const uint32_t sQ = sbase + Cfg::OFF_Q, sQb = sbase + Cfg::OFF_QB, sK = sbase + Cfg::OFF_K,
-                 sKb = sbase + Cfg::OFF_KB, sV = sbase + Cfg::OFF_V, sP = sbase + Cfg::OFF_P;
+                 sKb = sbase + Cfg::OFF_KB, sV = sbase + Cfg::OFF_V;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
   // barrier slots
   const uint32_t bar0 = smem_u32(bars);
@@ -118,7 +119,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tS = tmem, tO = tmem + 128;
+  const uint32_t tS = tmem + Cfg::T_S, tP = tmem + Cfg::T_P, tO = tmem + Cfg::T_O;
 
   if (warp == 4) {
     // ------------------------------------------------------------------ TMA producer
@@ -149,7 +150,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       constexpr uint32_t idO = instr_desc(kBf16, false, true, 128, D);
       // descriptor views built once; each MMA only adds a constant to the start-address field
       const DescBase dQ = kmajor_base<D>(sQ), dQb = kmajor_base<RPX>(sQb), dK = kmajor_base<D>(sK),
-                     dKb = kmajor_base<RPX>(sKb), dP = kmajor_base<128>(sP), dV = mnmajor_base<D>(sV);
+                     dKb = kmajor_base<RPX>(sKb), dV = mnmajor_base<D>(sV);
       auto issue_S = [&](int j) {
         const int ks = j % KST;
         mbar_wait(k_full + 8 * ks, (j / KST) & 1, abort_flag, a.status);
@@ -178,8 +179,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t vo = vs * Cfg::Q_BYTES;
 #pragma unroll
         for (int s = 0; s < 8; ++s)
-          umma_ss(tO, desc_at(dP, kmajor_step<128>(s)), desc_at(dV, vo + mnmajor_step<D>(s)), idO,
-                  (j > 0 || s > 0) ? 1u : 0u);
+          umma_ts(tO, tP + s * 8, desc_at(dV, vo + mnmajor_step<D>(s)), idO, (j > 0 || s > 0) ? 1u : 0u);
         umma_commit(pv_done);
         umma_commit(v_free + 8 * vs);
       }
@@ -191,7 +191,6 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
     const float sl2 = a.scale_log2;
     float m_used = -INFINITY, l = 0.f;
-    uint8_t* sP_gen = smem + Cfg::OFF_P;
     uint32_t ra[32], rb[32];  // two register buffers: the TMEM load of one chunk overlaps the math of the other
     for (int j = 0; j < n_kv; ++j) {
       const int k0 = j * 128;
@@ -270,15 +269,11 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             r[i] = __float_as_uint(p);
           }
         }
+        // P goes back to tensor memory as the A operand of O += P.V: 32 keys = 16 packed words
+        uint32_t w[16];
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint4 w;
-          w.x = Pack2<T>::pack(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]));
-          w.y = Pack2<T>::pack(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]));
-          w.z = Pack2<T>::pack(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
-          w.w = Pack2<T>::pack(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
-          *reinterpret_cast<uint4*>(sP_gen + tile_chunk_offset<128>(row, c * 32 + g * 8)) = w;
-        }
+        for (int i = 0; i < 16; ++i) w[i] = Pack2<T>::pack(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+        tmem_st16(tP + lane_off + c * 16, w);
       };
       tmem_wait_ld(ra);
       tmem_ld32(tSl + 32, rb);
@@ -292,7 +287,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tmem_wait_ld(rb);
       chunk_exp(rb, 3);
       l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
-      fence_proxy_async_smem();
+      tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(p_ready);
     }

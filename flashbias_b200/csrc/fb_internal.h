@@ -31,7 +31,8 @@ struct PackPlan {
   int Bq, Hq, Bk, Hk;
   size_t q_bytes, k_bytes;  // each rounded up to 256
 };
-bool plan_pack(const fb_params* p, PackPlan* plan);  // false if the rank does not fit the tensor path
+// false if the rank does not fit the tensor path; min_rp widens the packed width (16, 32 or 64)
+bool plan_pack(const fb_params* p, PackPlan* plan, int min_rp = 16);
 // kcenter (optional, same layout as kpack): k_bias minus the k_bias of the first key of each 128-key tile.
 int launch_pack(const fb_params* p, const PackPlan& plan, void* qpack, void* kpack, void* kcenter, cudaStream_t st);
 

@@ -18,7 +18,7 @@ static int pad_pow2_16(int x) {
   return r;
 }
 
-bool plan_pack(const fb_params* p, PackPlan* plan) {
+bool plan_pack(const fb_params* p, PackPlan* plan, int min_rp) {
   plan->Bq = p->q_bias_stride[0] == 0 ? 1 : p->B;
   plan->Hq = p->q_bias_stride[1] == 0 ? 1 : p->H;
   plan->Bk = p->k_bias_stride[0] == 0 ? 1 : p->B;
@@ -38,6 +38,7 @@ bool plan_pack(const fb_params* p, PackPlan* plan) {
   }
   // at least two column groups: the centred k-side copy used by the backward holds a (hi, lo) pair
   plan->RP = pad_pow2_16((plan->nsplit < 2 ? 2 : plan->nsplit) * p->R);
+  if (plan->RP < min_rp) plan->RP = min_rp;
   if (plan->RP > 64) return false;
   plan->q_bytes = round256((size_t)plan->Bq * plan->Hq * p->Sq * plan->RP * 2);
   plan->k_bytes = round256((size_t)plan->Bk * plan->Hk * p->Sk * plan->RP * 2);

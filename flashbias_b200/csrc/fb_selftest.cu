@@ -11,6 +11,7 @@ struct SelfCase {
   int mode;  // 0: A,B K-major via TMA (+ optional second pair of width c2) -> D = A B^T          (N = 128)
              // 1: A K-major written by threads, B MN-major via TMA          -> D = A B            (N = c)
              // 2: A MN-major written by threads, B MN-major via TMA         -> D = A^T B          (N = c)
+             // 3: A written to tensor memory by threads, B MN-major via TMA -> D = A B            (N = c)
   int c;
   int c2;
 };
@@ -19,6 +20,7 @@ static const SelfCase kCases[] = {
     {0, 16, 0}, {0, 32, 0}, {0, 64, 0}, {0, 128, 0}, {0, 32, 16}, {0, 64, 16}, {0, 64, 32}, {0, 128, 64},
     {1, 16, 0}, {1, 32, 0}, {1, 64, 0}, {1, 128, 0},
     {2, 16, 0}, {2, 32, 0}, {2, 64, 0}, {2, 128, 0},
+    {3, 32, 0}, {3, 64, 0}, {3, 128, 0},
 };
 static const int kNumCases = sizeof(kCases) / sizeof(kCases[0]);
 
@@ -57,10 +59,10 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
     mbar_fence_init();
   }
   if (warp == 0) {
-    tmem_alloc(smem_u32(tmem_slot), 128);
+    tmem_alloc(smem_u32(tmem_slot), 256);
     tmem_relinquish();
   }
-  if (MODE != 0) {
+  if (MODE == 1 || MODE == 2) {
     // thread t writes row t of the 128 x 128 A tile, 16-byte chunks, in the swizzled layout
     const uint4* src = reinterpret_cast<const uint4*>(a_glob + (size_t)tid * 128);
 #pragma unroll
@@ -73,6 +75,20 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
+  if (MODE == 3) {
+    // thread t stores row t of A (128 16-bit values = 64 words) into tensor-memory columns [128, 192)
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(a_glob + (size_t)tid * 128);
+    for (int c0 = 0; c0 < 64; c0 += 16) {
+      uint32_t r[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) r[i] = src[c0 + i];
+      tmem_st16(tmem + ((uint32_t)(warp * 32) << 16) + 128 + c0, r);
+    }
+    tmem_wait_st();
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+  }
 
   if (tid == 0) {
     uint32_t bytes = tile_bytes(C) + (MODE == 0 ? tile_bytes(C) : 0) + (C2 ? 2 * tile_bytes(C2 ? C2 : 16) : 0);
@@ -98,10 +114,14 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
       const uint32_t id = instr_desc(bf16 != 0, false, true, 128, N);
       for (int ks = 0; ks < 8; ++ks)
         umma_ss(tmem, desc_kmajor<128>(smem_u32(sA), ks * 16), desc_mnmajor<C>(smem_u32(sB), ks * 16), id, ks > 0);
-    } else {
+    } else if (MODE == 2) {
       const uint32_t id = instr_desc(bf16 != 0, true, true, 128, N);
       for (int ks = 0; ks < 8; ++ks)
         umma_ss(tmem, desc_mnmajor<128>(smem_u32(sA), ks * 16), desc_mnmajor<C>(smem_u32(sB), ks * 16), id, ks > 0);
+    } else {
+      const uint32_t id = instr_desc(bf16 != 0, false, true, 128, N);
+      for (int ks = 0; ks < 8; ++ks)
+        umma_ts(tmem, tmem + 128 + ks * 8, desc_mnmajor<C>(smem_u32(sB), ks * 16), id, ks > 0);
     }
     umma_commit(bar_mma);
   }
@@ -118,7 +138,7 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, 128);
+  if (warp == 0) tmem_dealloc(tmem, 256);
 }
 
 template <int MODE, int C, int C2>
@@ -185,6 +205,9 @@ extern "C" int fb_selftest_run(int case_id, int32_t dtype, const void* a, const 
     case 13: return run_case<2, 32, 0>(bf, a, b, d_out, status, st);
     case 14: return run_case<2, 64, 0>(bf, a, b, d_out, status, st);
     case 15: return run_case<2, 128, 0>(bf, a, b, d_out, status, st);
+    case 16: return run_case<3, 32, 0>(bf, a, b, d_out, status, st);
+    case 17: return run_case<3, 64, 0>(bf, a, b, d_out, status, st);
+    case 18: return run_case<3, 128, 0>(bf, a, b, d_out, status, st);
   }
   return FB_EINVAL_SHAPE;
 }
