@@ -173,7 +173,7 @@ extern "C" int fb_bwd_uses_tensor_path(const fb_params* p) {
 extern "C" size_t fb_fwd_workspace_bytes(const fb_params* p) {
   if (validate_common(p)) return 0;
   PackPlan plan;
-  if (fwd_sm100_supported(p, &plan)) return plan.q_bytes + plan.k_bytes;
+  if (fwd_sm100_supported(p, &plan)) return plan.q_bytes + plan.k_bytes + plan.qs_bytes;
   return 0;
 }
 
@@ -183,7 +183,7 @@ extern "C" int fb_fwd(const fb_params* p, void* cuda_stream) {
   cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
   PackPlan plan;
   if (fwd_sm100_supported(p, &plan)) {
-    if ((rc = check_workspace(p, plan.q_bytes + plan.k_bytes))) return rc;
+    if ((rc = check_workspace(p, plan.q_bytes + plan.k_bytes + plan.qs_bytes))) return rc;
     return launch_fwd_sm100(p, plan, st);
   }
   return launch_fwd_general(p, st);

@@ -23,10 +23,11 @@
 namespace fb {
 
 struct BwdArgs {
-  int B, H, Sq, Sk, nq_tiles, nk_tiles, causal, R, nsplit;
+  int B, H, Sq, Sk, nq_tiles, nk_tiles, causal, R;
   int hq_bcast, bq_bcast, hk_bcast, bk_bcast;
   int Hq, Hk;  // head extents of the un-expanded factors
-  float scale, scale_log2;
+  float dk_scale;    // applied to dK and dk_bias on store: the softmax scale unless it is already in the operands
+  float scale_log2;  // logits * log2(e) = S * scale_log2
   const float* lse;
   const float* delta;
   int64_t lse_stride_bh;
@@ -43,19 +44,22 @@ struct BwdArgs {
   __device__ __forceinline__ const T* k_bias_t() const { return reinterpret_cast<const T*>(k_bias); }
 };
 
-template <int D, int RP>
+template <int D, int RP, int NQ>
 struct BwdCfg {
   static constexpr int RPX = RP ? RP : 16;
+  static constexpr int D_BYTES = tile_bytes(D);
+  static constexpr int R_BYTES = RP ? tile_bytes(RPX) : 0;
+  // one stage: Q (or hi of q*scale), dO, Qb, then lo of q*scale when the query operand is split
+  static constexpr int STAGE_BYTES = (1 + NQ) * D_BYTES + R_BYTES;
+  static constexpr int OFF_QLO = 2 * D_BYTES + R_BYTES;
+  static constexpr int PDS_BYTES = 2 * tile_bytes(128);      // P then dS
   // P and dS tiles are double-buffered when shared memory allows it, so that the exponentials of
   // query tile i+1 overlap the dV/dK/dQ MMAs of query tile i.
-  static constexpr bool PIPE = (D == 32 && RP <= 32);
+  static constexpr bool PIPE =
+      (D == 32) && (2 * D_BYTES + 2 * R_BYTES + 2 * STAGE_BYTES + 2 * PDS_BYTES + 8192 <= 227 * 1024);
   static constexpr int NBUF = PIPE ? 2 : 1;
   // [Q|Qb] and [K|Kc] read as one MN-major operand of N = D + RP (two 64-byte-swizzled tiles)
   static constexpr bool MERGE = (D == 32 && RP == 32);
-  static constexpr int D_BYTES = tile_bytes(D);
-  static constexpr int R_BYTES = RP ? tile_bytes(RPX) : 0;
-  static constexpr int STAGE_BYTES = 2 * D_BYTES + R_BYTES;  // Q, dO, Qb
-  static constexpr int PDS_BYTES = 2 * tile_bytes(128);      // P then dS
   static constexpr int OFF_K = 0;
   static constexpr int OFF_KB = OFF_K + D_BYTES;
   static constexpr int OFF_KC = OFF_KB + R_BYTES;  // centered k_bias tile (dq_bias only)
@@ -70,16 +74,16 @@ struct BwdCfg {
   static constexpr int T_S = 0, T_DP = 128, T_DV = 256, T_DK = T_DV + D, T_DKB = T_DK + D, T_DQ = T_DKB + RP,
                        T_DQB = T_DQ + D, T_END = T_DQB + RP;
   static_assert(T_END <= 512, "tensor memory budget exceeded");
-  static_assert(SMEM <= 227 * 1024, "shared memory budget exceeded");
+  static constexpr bool FITS = SMEM <= 227 * 1024;  // otherwise the variant is not built (shape-generic kernels)
 };
 
 template <int C>
 __device__ __forceinline__ void tma_tile_bwd(uint32_t dst, const CUtensorMap* m, uint32_t bar, int row0, int h,
-                                             int b) {
+                                             int b, int col0 = 0) {
   constexpr int SWB = swizzle_bytes(C);
   constexpr int NB = C * 2 / SWB;
 #pragma unroll
-  for (int blk = 0; blk < NB; ++blk) tma_load_4d(dst + blk * 128 * SWB, m, bar, blk * (SWB / 2), row0, h, b);
+  for (int blk = 0; blk < NB; ++blk) tma_load_4d(dst + blk * 128 * SWB, m, bar, col0 + blk * (SWB / 2), row0, h, b);
 }
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
@@ -87,13 +91,13 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
                : "memory");
 }
 
-template <typename T, int D, int RP>
+template <typename T, int D, int RP, int NQ>
 __global__ void __launch_bounds__(320, 1)
 bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                  const __grid_constant__ CUtensorMap tmQb, const __grid_constant__ CUtensorMap tmKb,
                  const __grid_constant__ CUtensorMap tmKc, const BwdArgs a) {
-  using Cfg = BwdCfg<D, RP>;
+  using Cfg = BwdCfg<D, RP, NQ>;
   constexpr int RPX = Cfg::RPX;
   constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
   constexpr float kLog2e = 1.4426950408889634f;
@@ -167,6 +171,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tma_tile_bwd<D>(base, &tmQ, qdo_full + 8 * st, q0, h, b);
         tma_tile_bwd<D>(base + Cfg::D_BYTES, &tmDO, qdo_full + 8 * st, q0, h, b);
         if (RP) tma_tile_bwd<RPX>(base + 2 * Cfg::D_BYTES, &tmQb, qdo_full + 8 * st, q0, hq, bq);
+        if (NQ == 2) tma_tile_bwd<D>(base + Cfg::OFF_QLO, &tmQ, qdo_full + 8 * st, q0, h, b, D);
       }
     }
   } else if (warp == 9) {
@@ -196,13 +201,19 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t so = st * Cfg::STAGE_BYTES;
         mbar_wait(qdo_full + 8 * st, (it >> 1) & 1, abort_flag, a.status);
         tc_fence_after_sync();
-#pragma unroll
-        for (int s = 0; s < D / 16; ++s)
-          umma_ss(tmem + Cfg::T_S, desc_at(kQ, so + kmajor_step<D>(s)), desc_at(kK, kmajor_step<D>(s)), idS, s > 0);
+        // bias products first, into the empty accumulator (large factor terms cancel among themselves)
         if (RP) {
 #pragma unroll
           for (int s = 0; s < RPX / 16; ++s)
-            umma_ss(tmem + Cfg::T_S, desc_at(kQb, so + kmajor_step<RPX>(s)), desc_at(kKb, kmajor_step<RPX>(s)), idS, 1);
+            umma_ss(tmem + Cfg::T_S, desc_at(kQb, so + kmajor_step<RPX>(s)), desc_at(kKb, kmajor_step<RPX>(s)), idS,
+                    s > 0);
+        }
+#pragma unroll
+        for (int t = 0; t < NQ; ++t) {  // query terms share the K tile
+#pragma unroll
+          for (int s = 0; s < D / 16; ++s)
+            umma_ss(tmem + Cfg::T_S, desc_at(kQ, so + (t ? Cfg::OFF_QLO : 0) + kmajor_step<D>(s)),
+                    desc_at(kK, kmajor_step<D>(s)), idS, (RP || t > 0 || s > 0) ? 1u : 0u);
         }
         umma_commit(s_full);
 #pragma unroll
@@ -237,6 +248,9 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               umma_ss(tmem + Cfg::T_DKB, desc_at(mDS, po + mnmajor_step<128>(s)),
                       desc_at(mQb, so + mnmajor_step<RPX>(s)), idTR, acc);
           }
+          if (NQ == 2)  // dK += dS^T . lo(q*scale)
+            umma_ss(tmem + Cfg::T_DK, desc_at(mDS, po + mnmajor_step<128>(s)),
+                    desc_at(mQ, so + Cfg::OFF_QLO + mnmajor_step<D>(s)), idTD, 1);
         }
         if (it > 0) {
           mbar_wait(dq_drained, (it - 1) & 1, abort_flag, a.status);
@@ -454,10 +468,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             wv.y = Pack2<T>::pack(__uint_as_float(rv[g * 8 + 2]), __uint_as_float(rv[g * 8 + 3]));
             wv.z = Pack2<T>::pack(__uint_as_float(rv[g * 8 + 4]), __uint_as_float(rv[g * 8 + 5]));
             wv.w = Pack2<T>::pack(__uint_as_float(rv[g * 8 + 6]), __uint_as_float(rv[g * 8 + 7]));
-            wk.x = Pack2<T>::pack(__uint_as_float(rk[g * 8 + 0]) * a.scale, __uint_as_float(rk[g * 8 + 1]) * a.scale);
-            wk.y = Pack2<T>::pack(__uint_as_float(rk[g * 8 + 2]) * a.scale, __uint_as_float(rk[g * 8 + 3]) * a.scale);
-            wk.z = Pack2<T>::pack(__uint_as_float(rk[g * 8 + 4]) * a.scale, __uint_as_float(rk[g * 8 + 5]) * a.scale);
-            wk.w = Pack2<T>::pack(__uint_as_float(rk[g * 8 + 6]) * a.scale, __uint_as_float(rk[g * 8 + 7]) * a.scale);
+            wk.x = Pack2<T>::pack(__uint_as_float(rk[g * 8 + 0]) * a.dk_scale, __uint_as_float(rk[g * 8 + 1]) * a.dk_scale);
+            wk.y = Pack2<T>::pack(__uint_as_float(rk[g * 8 + 2]) * a.dk_scale, __uint_as_float(rk[g * 8 + 3]) * a.dk_scale);
+            wk.z = Pack2<T>::pack(__uint_as_float(rk[g * 8 + 4]) * a.dk_scale, __uint_as_float(rk[g * 8 + 5]) * a.dk_scale);
+            wk.w = Pack2<T>::pack(__uint_as_float(rk[g * 8 + 6]) * a.dk_scale, __uint_as_float(rk[g * 8 + 7]) * a.dk_scale);
             *reinterpret_cast<uint4*>(dvrow + c0 + g * 8) = wv;
             *reinterpret_cast<uint4*>(dkrow + c0 + g * 8) = wk;
           }
@@ -467,7 +481,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (RP && wg == 0) {
       const int bk = a.bk_bcast ? 0 : b, hk = a.hk_bcast ? 0 : h;
       float* dst = a.dkb_acc + (((int64_t)bk * a.Sk + krow) * a.Hk + hk) * a.R;
-      const int used = a.nsplit * a.R;
+      const int used = a.R;
 #pragma unroll 1
       for (int c0 = 0; c0 < RPX && c0 < used; c0 += 16) {
         uint32_t r[16];
@@ -476,7 +490,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (krow < a.Sk) {
 #pragma unroll
           for (int i = 0; i < 16; ++i)
-            if (c0 + i < used) atomicAdd(dst + (c0 + i) % a.R, __uint_as_float(r[i]) * a.scale);
+            if (c0 + i < used) atomicAdd(dst + c0 + i, __uint_as_float(r[i]) * a.dk_scale);
         }
       }
     }
@@ -537,14 +551,15 @@ static bool rows_16b_ok(const void* ptr, const int64_t* st) {
 }
 
 struct BwdWs {
-  size_t off_qpack, off_kpack, off_kcenter, off_dq, off_dqb, off_dkb, total, zero_bytes;
+  size_t off_qpack, off_kpack, off_kcenter, off_qs, off_dq, off_dqb, off_dkb, total, zero_bytes;
 };
 static BwdWs bwd_layout(const fb_params* p, const PackPlan& plan) {
   BwdWs w;
   w.off_qpack = 0;
   w.off_kpack = plan.q_bytes;
   w.off_kcenter = w.off_kpack + plan.k_bytes;
-  w.off_dq = w.off_kcenter + plan.k_bytes;
+  w.off_qs = w.off_kcenter + plan.k_bytes;
+  w.off_dq = w.off_qs + plan.qs_bytes;
   const size_t dq = round256((size_t)p->B * p->Sq * p->H * p->D * 4);
   const size_t dqb = p->R ? round256((size_t)plan.Bq * p->Sq * plan.Hq * p->R * 4) : 0;
   const size_t dkb = p->R ? round256((size_t)plan.Bk * p->Sk * plan.Hk * p->R * 4) : 0;
@@ -560,10 +575,9 @@ bool bwd_sm100_supported(const fb_params* p, PackPlan* plan) {
   if (p->mask_kind != FB_MASK_NONE) return false;
   if (!(p->D == 32 || p->D == 64)) return false;
   if (!(p->softmax_scale > 0.f) || !isfinite(p->softmax_scale)) return false;
-  // head_dim 32: packed factors as wide as the head (32 columns), so that [Q|Qb] and [K|Kc] are pairs of
-  // equally laid-out tiles and dK|dk_bias, dQ|dq_bias are single MMAs of N = 64
-  if (!plan_pack(p, plan, p->D == 32 ? 32 : 16)) return false;
+  if (!plan_pack(p, plan, true)) return false;
   if (256 + 3 * p->D + 2 * plan->RP > 512) return false;
+  if (p->D == 64 && plan->RP == 32 && plan->nq == 2) return false;  // tiles exceed the shared memory of an SM
   if (!tma_compatible(p->q, p->q_stride[2], p->q_stride[1], p->q_stride[0], p->H, p->B)) return false;
   if (!tma_compatible(p->k, p->k_stride[2], p->k_stride[1], p->k_stride[0], p->H, p->B)) return false;
   if (!tma_compatible(p->v, p->v_stride[2], p->v_stride[1], p->v_stride[0], p->H, p->B)) return false;
@@ -578,9 +592,12 @@ bool bwd_sm100_supported(const fb_params* p, PackPlan* plan) {
 
 size_t bwd_sm100_workspace(const fb_params* p, const PackPlan& plan) { return bwd_layout(p, plan).total; }
 
-template <typename T, int D, int RP>
+template <typename T, int D, int RP, int NQ>
 static int launch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
-  using Cfg = BwdCfg<D, RP>;
+  using Cfg = BwdCfg<D, RP, NQ>;
+  if constexpr (!Cfg::FITS) {
+    return FB_ENOTBUILT;
+  } else {
   int rc;
   const BwdWs w = bwd_layout(p, plan);
   uint8_t* ws = reinterpret_cast<uint8_t*>(p->workspace);
@@ -593,8 +610,17 @@ static int launch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t s
   cudaError_t e = cudaMemsetAsync(ws + w.off_dq, 0, w.zero_bytes, st);
   if (e != cudaSuccess) return (int)e;
   CUtensorMap tQ, tK, tV, tDO, tQb, tKb, tKc;
-  if ((rc = make_tmap_4d(&tQ, p->q, D, p->Sq, p->H, p->B, p->q_stride[2], p->q_stride[1], p->q_stride[0], D, 128)))
+  if (NQ == 2) {
+    // query operand = (hi, lo) of q*scale, laid out (B, H, Sq, 2D) in the workspace
+    void* qs = ws + w.off_qs;
+    if ((rc = launch_pack_qscaled(p, plan, qs, st))) return rc;
+    if ((rc = make_tmap_4d(&tQ, qs, 2 * D, p->Sq, p->H, p->B, 2 * D, (int64_t)2 * D * p->Sq,
+                           (int64_t)2 * D * p->Sq * p->H, D, 128)))
+      return rc;
+  } else if ((rc = make_tmap_4d(&tQ, p->q, D, p->Sq, p->H, p->B, p->q_stride[2], p->q_stride[1], p->q_stride[0], D,
+                                128))) {
     return rc;
+  }
   if ((rc = make_tmap_4d(&tK, p->k, D, p->Sk, p->H, p->B, p->k_stride[2], p->k_stride[1], p->k_stride[0], D, 128)))
     return rc;
   if ((rc = make_tmap_4d(&tV, p->v, D, p->Sk, p->H, p->B, p->v_stride[2], p->v_stride[1], p->v_stride[0], D, 128)))
@@ -623,11 +649,11 @@ static int launch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t s
   a.nk_tiles = (p->Sk + 127) / 128;
   a.causal = p->causal;
   a.R = p->R;
-  a.nsplit = plan.nsplit;
   a.hq_bcast = plan.Hq == 1; a.bq_bcast = plan.Bq == 1; a.hk_bcast = plan.Hk == 1; a.bk_bcast = plan.Bk == 1;
   a.Hq = plan.Hq; a.Hk = plan.Hk;
-  a.scale = p->softmax_scale;
-  a.scale_log2 = p->softmax_scale * 1.4426950408889634f;
+  // with a split query operand the scale is already inside S and inside the operands of dK / dk_bias
+  a.dk_scale = NQ == 2 ? 1.f : p->softmax_scale;
+  a.scale_log2 = (NQ == 2 ? 1.f : p->softmax_scale) * 1.4426950408889634f;
   a.lse = p->lse;
   a.delta = p->delta;
   a.lse_stride_bh = p->lse_stride_bh;
@@ -643,7 +669,7 @@ static int launch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t s
   a.k_bias = p->k_bias;
   for (int i = 0; i < 3; ++i) a.kb_stride[i] = p->k_bias_stride[i];
   a.status = p->status;
-  auto kern = bwd_sm100_kernel<T, D, RP>;
+  auto kern = bwd_sm100_kernel<T, D, RP, NQ>;
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -666,12 +692,14 @@ static int launch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t s
   if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
   if (p->R > 0) return store_factor_grads_from(p, a.dqb_acc, a.dkb_acc, st);
   return 0;
+  }
 }
 
 template <typename T>
 static int dispatch_bwd(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
-#define FB_CASE(DD, RR) \
-  if (p->D == DD && plan.RP == RR) return launch_bwd_t<T, DD, RR>(p, plan, st);
+#define FB_CASE(DD, RR)                                                              \
+  if (p->D == DD && plan.RP == RR)                                                   \
+    return plan.nq == 2 ? launch_bwd_t<T, DD, RR, 2>(p, plan, st) : launch_bwd_t<T, DD, RR, 1>(p, plan, st);
   FB_CASE(32, 0) FB_CASE(32, 16) FB_CASE(32, 32) FB_CASE(32, 64)
   FB_CASE(64, 0) FB_CASE(64, 16) FB_CASE(64, 32)
 #undef FB_CASE

@@ -30,16 +30,21 @@ struct FwdArgs {
   int* status;
 };
 
-template <int D, int RP>
+template <int D, int RP, int NQ>
 struct FwdCfg {
   // (K stages, V stages, CTAs per SM) chosen so that the tiles fit the shared memory of the SM
-  static constexpr int KST = 2;
-  static constexpr int VST = 2;
   static constexpr int MINB = (D == 128) ? 1 : 2;
+  // as many K|Kb and V stages (up to 4) as fit beside Q in the shared memory of one of MINB co-resident CTAs:
+  // the TMA producer runs that many key tiles ahead, which is what hides the L2/HBM latency of the loads
+  static constexpr int BUDGET = (MINB == 2 ? 110 : 220) * 1024 - 2048;
+  static constexpr int PER_STAGE = 2 * tile_bytes(D) + (RP ? tile_bytes(RP ? RP : 16) : 0);
+  static constexpr int FIT = (BUDGET - NQ * tile_bytes(D) - (RP ? tile_bytes(RP ? RP : 16) : 0)) / PER_STAGE;
+  static constexpr int KST = FIT >= 4 ? 4 : (FIT >= 2 ? FIT : 2);
+  static constexpr int VST = KST;
   static constexpr int Q_BYTES = tile_bytes(D);
   static constexpr int QB_BYTES = RP ? tile_bytes(RP ? RP : 16) : 0;
   static constexpr int OFF_Q = 0;
-  static constexpr int OFF_QB = OFF_Q + Q_BYTES;
+  static constexpr int OFF_QB = OFF_Q + NQ * Q_BYTES;  // NQ query terms (q, or hi and lo of q*scale), then Qb
   static constexpr int OFF_K = OFF_QB + QB_BYTES;
   static constexpr int OFF_KB = OFF_K + KST * Q_BYTES;
   static constexpr int OFF_V = OFF_KB + KST * QB_BYTES;
@@ -51,19 +56,20 @@ struct FwdCfg {
 };
 
 template <int C>
-__device__ __forceinline__ void tma_tile_4d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int row0, int h, int b) {
+__device__ __forceinline__ void tma_tile_4d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int row0, int h, int b,
+                                            int col0 = 0) {
   constexpr int SWB = swizzle_bytes(C);
   constexpr int NB = C * 2 / SWB;
 #pragma unroll
-  for (int blk = 0; blk < NB; ++blk) tma_load_4d(dst + blk * 128 * SWB, m, bar, blk * (SWB / 2), row0, h, b);
+  for (int blk = 0; blk < NB; ++blk) tma_load_4d(dst + blk * 128 * SWB, m, bar, col0 + blk * (SWB / 2), row0, h, b);
 }
 
-template <typename T, int D, int RP>
-__global__ void __launch_bounds__(192, FwdCfg<D, RP>::MINB)
+template <typename T, int D, int RP, int NQ>
+__global__ void __launch_bounds__(192, FwdCfg<D, RP, NQ>::MINB)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmQb,
                  const __grid_constant__ CUtensorMap tmKb, const FwdArgs a) {
-  using Cfg = FwdCfg<D, RP>;
+  using Cfg = FwdCfg<D, RP, NQ>;
   constexpr int KST = Cfg::KST, VST = Cfg::VST;
   constexpr int RPX = RP ? RP : 16;  // keeps templates well-formed when there is no bias
   constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
@@ -77,9 +83,9 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   // barrier slots
   const uint32_t bar0 = smem_u32(bars);
   const uint32_t q_full = bar0, s_full = bar0 + 8, p_ready = bar0 + 16, pv_done = bar0 + 24;
-  const uint32_t k_full = bar0 + 32, k_free = bar0 + 48, v_full = bar0 + 64, v_free = bar0 + 80;  // 2 slots each
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::OFF_BAR + 96);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::OFF_BAR + 104);
+  const uint32_t k_full = bar0 + 32, k_free = bar0 + 64, v_full = bar0 + 96, v_free = bar0 + 128;  // 4 slots each
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::OFF_BAR + 160);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::OFF_BAR + 168);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int BH = a.B * a.H;
@@ -101,9 +107,9 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       *abort_flag = 0;
       mbar_init(q_full, 1);
       mbar_init(s_full, 1);
-      mbar_init(p_ready, 128);
+      mbar_init(p_ready, 4);  // one arrival per softmax warp
       mbar_init(pv_done, 1);
-      for (int i = 0; i < 2; ++i) {
+      for (int i = 0; i < 4; ++i) {
         mbar_init(k_full + 8 * i, 1);
         mbar_init(k_free + 8 * i, 1);
         mbar_init(v_full + 8 * i, 1);
@@ -129,8 +135,9 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tma_prefetch_desc(&tmV);
       const int hq = a.hq_bcast ? 0 : h, bq = a.bq_bcast ? 0 : b;
       const int hk = a.hk_bcast ? 0 : h, bk = a.bk_bcast ? 0 : b;
-      mbar_expect_tx(q_full, Cfg::Q_BYTES + Cfg::QB_BYTES);
-      tma_tile_4d<D>(sQ, &tmQ, q_full, q0, h, b);
+      mbar_expect_tx(q_full, NQ * Cfg::Q_BYTES + Cfg::QB_BYTES);
+#pragma unroll
+      for (int t = 0; t < NQ; ++t) tma_tile_4d<D>(sQ + t * Cfg::Q_BYTES, &tmQ, q_full, q0, h, b, t * D);
       if (RP) tma_tile_4d<RPX>(sQb, &tmQb, q_full, q0, hq, bq);
       for (int j = 0; j < n_kv; ++j) {
         const int ks = j % KST, vs = j % VST;
@@ -156,13 +163,20 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         mbar_wait(k_full + 8 * ks, (j / KST) & 1, abort_flag, a.status);
         tc_fence_after_sync();
         const uint32_t ko = ks * Cfg::Q_BYTES, kbo = ks * Cfg::QB_BYTES;
-#pragma unroll
-        for (int s = 0; s < D / 16; ++s)
-          umma_ss(tS, desc_at(dQ, kmajor_step<D>(s)), desc_at(dK, ko + kmajor_step<D>(s)), idS, s > 0);
+        // The bias products go first, into the empty accumulator: factor terms as large as a sequence
+        // position then only meet each other (and cancel exactly), instead of forcing the small q.k sum to be
+        // aligned to their magnitude inside the tensor core's adder.
         if (RP) {
 #pragma unroll
           for (int s = 0; s < RPX / 16; ++s)
-            umma_ss(tS, desc_at(dQb, kmajor_step<RPX>(s)), desc_at(dKb, kbo + kmajor_step<RPX>(s)), idS, 1);
+            umma_ss(tS, desc_at(dQb, kmajor_step<RPX>(s)), desc_at(dKb, kbo + kmajor_step<RPX>(s)), idS, s > 0);
+        }
+#pragma unroll
+        for (int t = 0; t < NQ; ++t) {  // query terms share the K tile
+#pragma unroll
+          for (int s = 0; s < D / 16; ++s)
+            umma_ss(tS, desc_at(dQ, t * Cfg::Q_BYTES + kmajor_step<D>(s)), desc_at(dK, ko + kmajor_step<D>(s)), idS,
+                    (RP || t > 0 || s > 0) ? 1u : 0u);
         }
         umma_commit(s_full);
         umma_commit(k_free + 8 * ks);
@@ -289,7 +303,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       tmem_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(p_ready);
+      mbar_arrive_warp(p_ready);
     }
     // ---- epilogue: O / l -> global, lse
     mbar_wait(pv_done, (n_kv - 1) & 1, abort_flag, a.status);
@@ -348,20 +362,29 @@ bool fwd_sm100_supported(const fb_params* p, PackPlan* plan) {
   return plan_pack(p, plan);
 }
 
-template <typename T, int D, int RP>
+template <typename T, int D, int RP, int NQ>
 static int launch_fwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
-  using Cfg = FwdCfg<D, RP>;
+  using Cfg = FwdCfg<D, RP, NQ>;
   int rc;
   uint8_t* ws = reinterpret_cast<uint8_t*>(p->workspace);
   void* qpack = ws;
   void* kpack = ws + plan.q_bytes;
+  void* qs = ws + plan.q_bytes + plan.k_bytes;
   if (RP) {
     if ((rc = launch_pack(p, plan, qpack, kpack, nullptr, st))) return rc;
   }
   CUtensorMap tQ, tK, tV, tQb, tKb;
   constexpr int BOXD = D > 64 ? 64 : D;
-  if ((rc = make_tmap_4d(&tQ, p->q, D, p->Sq, p->H, p->B, p->q_stride[2], p->q_stride[1], p->q_stride[0], BOXD, 128)))
+  if (NQ == 2) {
+    // query operand = (hi, lo) of q*scale, laid out (B, H, Sq, 2D) in the workspace
+    if ((rc = launch_pack_qscaled(p, plan, qs, st))) return rc;
+    if ((rc = make_tmap_4d(&tQ, qs, 2 * D, p->Sq, p->H, p->B, 2 * D, (int64_t)2 * D * p->Sq,
+                           (int64_t)2 * D * p->Sq * p->H, BOXD, 128)))
+      return rc;
+  } else if ((rc = make_tmap_4d(&tQ, p->q, D, p->Sq, p->H, p->B, p->q_stride[2], p->q_stride[1], p->q_stride[0], BOXD,
+                                128))) {
     return rc;
+  }
   if ((rc = make_tmap_4d(&tK, p->k, D, p->Sk, p->H, p->B, p->k_stride[2], p->k_stride[1], p->k_stride[0], BOXD, 128)))
     return rc;
   if ((rc = make_tmap_4d(&tV, p->v, D, p->Sk, p->H, p->B, p->v_stride[2], p->v_stride[1], p->v_stride[0], BOXD, 128)))
@@ -382,14 +405,15 @@ static int launch_fwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t s
   a.nq_tiles = (p->Sq + 127) / 128;
   a.causal = p->causal;
   a.hq_bcast = plan.Hq == 1; a.bq_bcast = plan.Bq == 1; a.hk_bcast = plan.Hk == 1; a.bk_bcast = plan.Bk == 1;
-  a.scale = p->softmax_scale;
-  a.scale_log2 = p->softmax_scale * 1.4426950408889634f;
+  // logits = a.scale * S: the scale is already inside the query operand when it is split
+  a.scale = NQ == 2 ? 1.f : p->softmax_scale;
+  a.scale_log2 = a.scale * 1.4426950408889634f;
   a.o = p->o;
   for (int i = 0; i < 3; ++i) a.o_stride[i] = p->o_stride[i];
   a.lse = p->lse;
   a.lse_stride_bh = p->lse_stride_bh;
   a.status = p->status;
-  auto kern = fwd_sm100_kernel<T, D, RP>;
+  auto kern = fwd_sm100_kernel<T, D, RP, NQ>;
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -408,8 +432,9 @@ static int launch_fwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t s
 
 template <typename T>
 static int dispatch_fwd(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
-#define FB_CASE(DD, RR) \
-  if (p->D == DD && plan.RP == RR) return launch_fwd_t<T, DD, RR>(p, plan, st);
+#define FB_CASE(DD, RR)                                                              \
+  if (p->D == DD && plan.RP == RR)                                                   \
+    return plan.nq == 2 ? launch_fwd_t<T, DD, RR, 2>(p, plan, st) : launch_fwd_t<T, DD, RR, 1>(p, plan, st);
   FB_CASE(32, 0) FB_CASE(32, 16) FB_CASE(32, 32) FB_CASE(32, 64)
   FB_CASE(64, 0) FB_CASE(64, 16) FB_CASE(64, 32) FB_CASE(64, 64)
   FB_CASE(128, 0) FB_CASE(128, 16) FB_CASE(128, 32) FB_CASE(128, 64)

@@ -20,21 +20,25 @@ int make_tmap_4d(CUtensorMap* out, const void* ptr, int cols, int64_t rows, int6
 bool tma_compatible(const void* ptr, int64_t stride_row, int64_t stride_head, int64_t stride_batch, int64_t heads,
                     int64_t batch);
 
-// ---- packed bias factors ----------------------------------------------------------------------
-// The tensor-core kernels contract over [head_dim | packed rank].  The packed q-side factor holds
-// q_bias / softmax_scale split into `nsplit` 16-bit terms (hi, mid, lo) so that the fp32 sum of the
-// products reproduces the unscaled bias term; the k-side factor is repeated `nsplit` times.
-// Packed layout: (Bb, Hb, S, RP) contiguous, Bb/Hb = 1 on broadcast dims, RP = packed width.
+// ---- operand preparation (fb_pack.cu) ------------------------------------------------------------
+// The tensor-core kernels contract over [scaled query terms | packed rank] in one fp32 accumulator.
+//   nq == 1 (softmax_scale an exact power of two): the query operand is the caller's q, the q-side factor is
+//           q_bias / scale (exact), logits = scale * S.
+//   nq == 2: the query operand is q*scale as a (hi, lo) pair of 16-bit terms, laid out (B, H, Sq, 2D); factors
+//           are used as given, logits = S.
+// Packed factors: (Bb, Hb, S, RP) contiguous, Bb/Hb = 1 on broadcast dims, zero-padded to RP columns.
 struct PackPlan {
-  int nsplit;  // 1 when softmax_scale is an exact power of two, else 2 or 3
-  int RP;      // packed width: 0 (no bias), 16, 32 or 64
+  int nq;          // 1 or 2 query terms
+  float qb_mult;   // multiplier applied to q_bias when packing (1/scale when nq == 1)
+  int RP;          // packed factor width: 0 (no bias), 16, 32 or 64
   int Bq, Hq, Bk, Hk;
-  size_t q_bytes, k_bytes;  // each rounded up to 256
+  size_t q_bytes, k_bytes, qs_bytes;  // packed q factor, packed k factor, scaled-query copy (each rounded to 256)
 };
-// false if the rank does not fit the tensor path; min_rp widens the packed width (16, 32 or 64)
-bool plan_pack(const fb_params* p, PackPlan* plan, int min_rp = 16);
-// kcenter (optional, same layout as kpack): k_bias minus the k_bias of the first key of each 128-key tile.
+// false if the rank does not fit the tensor path; for_bwd reserves room for the centred (hi, lo) k-side copy
+bool plan_pack(const fb_params* p, PackPlan* plan, bool for_bwd = false);
+// kcenter (optional, same layout as kpack): k_bias minus the k_bias of the middle key of each group of 32 keys.
 int launch_pack(const fb_params* p, const PackPlan& plan, void* qpack, void* kpack, void* kcenter, cudaStream_t st);
+int launch_pack_qscaled(const fb_params* p, const PackPlan& plan, void* qs, cudaStream_t st);
 
 // ---- kernels ------------------------------------------------------------------------------------
 int launch_fwd_general(const fb_params* p, cudaStream_t st);

@@ -1,10 +1,14 @@
-// Packing of the low-rank bias factors into tensor-core operand columns.
+// Operand preparation for the tensor-core kernels.
 //
-// The tensor-core kernels accumulate  S' = q.k + qp.kp  in one fp32 accumulator and apply the
-// softmax scale afterwards, so the q-side factor is divided by the scale first.  To keep the
-// unscaled bias term exact to fp32 level, q_bias/scale is split into `nsplit` 16-bit terms
-// (x = hi + mid + lo, each the rounding of the running remainder) stored side by side, and the
-// k-side factor is repeated under each term.  Columns beyond nsplit*R are zero.
+// The kernels accumulate all logit terms in ONE fp32 accumulator,  S = qs.k + qb.kb,  where the softmax
+// scale has to live inside an operand:
+//   * scale an exact power of two: qs = q (the caller's tensor, untouched) and qb = q_bias / scale,
+//     which is exact in the 16-bit type; the exponent argument is S * scale * log2(e);
+//   * otherwise: qs = q * scale, stored as a (hi, lo) pair of 16-bit terms (contraction 2*head_dim),
+//     and qb = q_bias as given, so that the products of the bias factors stay exact and un-scaled --
+//     terms as large as an ALiBi position cancel inside one MMA instead of being rounded first.
+// Factors are zero-padded to RP columns (16/32/64).  The backward also gets a centred k-side copy
+// (k_bias minus the k_bias of the middle key of its group of 32 keys, as a (hi, lo) pair).
 #include <math.h>
 
 #include "fb_common.cuh"
@@ -18,27 +22,23 @@ static int pad_pow2_16(int x) {
   return r;
 }
 
-bool plan_pack(const fb_params* p, PackPlan* plan, int min_rp) {
+bool plan_pack(const fb_params* p, PackPlan* plan, bool for_bwd) {
   plan->Bq = p->q_bias_stride[0] == 0 ? 1 : p->B;
   plan->Hq = p->q_bias_stride[1] == 0 ? 1 : p->H;
   plan->Bk = p->k_bias_stride[0] == 0 ? 1 : p->B;
   plan->Hk = p->k_bias_stride[1] == 0 ? 1 : p->H;
+  int e;
+  const bool pow2 = frexpf(p->softmax_scale, &e) == 0.5f;
+  plan->nq = pow2 ? 1 : 2;
+  plan->qb_mult = pow2 ? (float)(1.0 / (double)p->softmax_scale) : 1.f;
+  plan->qs_bytes = pow2 ? 0 : round256((size_t)p->B * p->H * p->Sq * 2 * p->D * 2);
   if (p->R <= 0) {
-    plan->nsplit = 1;
     plan->RP = 0;
     plan->q_bytes = plan->k_bytes = 0;
     return true;
   }
-  int e;
-  const bool pow2 = frexpf(p->softmax_scale, &e) == 0.5f;
-  if (pow2) {
-    plan->nsplit = 1;
-  } else {
-    plan->nsplit = pad_pow2_16(3 * p->R) == pad_pow2_16(2 * p->R) ? 3 : 2;
-  }
-  // at least two column groups: the centred k-side copy used by the backward holds a (hi, lo) pair
-  plan->RP = pad_pow2_16((plan->nsplit < 2 ? 2 : plan->nsplit) * p->R);
-  if (plan->RP < min_rp) plan->RP = min_rp;
+  // the centred k-side copy of the backward holds a (hi, lo) pair: twice the rank
+  plan->RP = pad_pow2_16(for_bwd ? 2 * p->R : p->R);
   if (plan->RP > 64) return false;
   plan->q_bytes = round256((size_t)plan->Bq * plan->Hq * p->Sq * plan->RP * 2);
   plan->k_bytes = round256((size_t)plan->Bk * plan->Hk * p->Sk * plan->RP * 2);
@@ -47,9 +47,9 @@ bool plan_pack(const fb_params* p, PackPlan* plan, int min_rp) {
 
 template <typename T>
 __global__ void __launch_bounds__(256) pack_factor_kernel(const T* __restrict__ src, int64_t sb, int64_t sh, int64_t ss,
-                                                          int Bx, int Hx, int S, int R, int RP, int nsplit,
-                                                          float mult, int split, T* __restrict__ dst,
-                                                          T* __restrict__ dst_centered, int* status) {
+                                                          int Bx, int Hx, int S, int R, int RP, float mult,
+                                                          T* __restrict__ dst, T* __restrict__ dst_centered,
+                                                          int* status) {
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // (b, h, s)
   const int64_t total = (int64_t)Bx * Hx * S;
   if (idx >= total) return;
@@ -58,7 +58,16 @@ __global__ void __launch_bounds__(256) pack_factor_kernel(const T* __restrict__ 
   const int b = (int)(idx / ((int64_t)S * Hx));
   const T* in = src + b * sb + h * sh + s * ss;
   T* out = dst + idx * RP;
-  for (int c = nsplit * R; c < RP; ++c) out[c] = from_f32<T>(0.f);
+  for (int c = 0; c < RP; ++c) {
+    if (c < R) {
+      const float x = to_f32(in[c]);
+      const T y = from_f32<T>(x * mult);  // mult is 1 or a power of two: exact unless it overflows
+      if (!isfinite(to_f32(y)) && isfinite(x) && status) atomicExch(status, FB_DEV_FACTOR_OVERFLOW);
+      out[c] = y;
+    } else {
+      out[c] = from_f32<T>(0.f);
+    }
+  }
   if (dst_centered) {
     // k-side factor minus the factor of the middle key of its group of 32 keys: small-magnitude copy used
     // for dq_bias = dS.k_bias (the removed constant is re-applied in fp32 through the row sum of dS)
@@ -74,35 +83,48 @@ __global__ void __launch_bounds__(256) pack_factor_kernel(const T* __restrict__ 
       outc[R + c] = from_f32<T>(x - to_f32(hi));
     }
   }
-  for (int r = 0; r < R; ++r) {
-    const T raw = in[r];
-    if (!split) {
-      for (int t = 0; t < nsplit; ++t) out[t * R + r] = raw;
-    } else {
-      float rem = to_f32(raw) * mult;
-      for (int t = 0; t < nsplit; ++t) {
-        const T term = from_f32<T>(rem);
-        const float tf = to_f32(term);
-        if (t == 0 && !isfinite(tf) && isfinite(to_f32(raw)) && status) atomicExch(status, FB_DEV_FACTOR_OVERFLOW);
-        out[t * R + r] = term;
-        rem -= tf;
-      }
-    }
+}
+
+// qs[b][h][s][0:D] = T(q * scale), qs[b][h][s][D:2D] = T(q * scale - hi): the scaled query as two 16-bit terms.
+// One thread converts 8 consecutive elements (16-byte load, two 16-byte stores).
+template <typename T>
+__global__ void __launch_bounds__(256) pack_qscaled_kernel(const T* __restrict__ q, int64_t sb, int64_t sh, int64_t ss,
+                                                           int B, int H, int S, int D, float scale,
+                                                           T* __restrict__ qs) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // (b, h, s, d/8)
+  const int d8 = D / 8;
+  const int64_t total = (int64_t)B * H * S * d8;
+  if (idx >= total) return;
+  const int c = (int)(idx % d8);
+  const int s = (int)((idx / d8) % S);
+  const int h = (int)((idx / ((int64_t)d8 * S)) % H);
+  const int b = (int)(idx / ((int64_t)d8 * S * H));
+  const uint4 raw = *reinterpret_cast<const uint4*>(q + b * sb + h * sh + s * ss + c * 8);
+  const T* x = reinterpret_cast<const T*>(&raw);
+  uint4 hi4, lo4;
+  T* hi = reinterpret_cast<T*>(&hi4);
+  T* lo = reinterpret_cast<T*>(&lo4);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float v = to_f32(x[e]) * scale;
+    hi[e] = from_f32<T>(v);
+    lo[e] = from_f32<T>(v - to_f32(hi[e]));
   }
+  T* row = qs + (((int64_t)b * H + h) * S + s) * (2 * D);
+  *reinterpret_cast<uint4*>(row + c * 8) = hi4;
+  *reinterpret_cast<uint4*>(row + D + c * 8) = lo4;
 }
 
 template <typename T>
 static int launch_pack_t(const fb_params* p, const PackPlan& plan, void* qpack, void* kpack, void* kcenter,
                          cudaStream_t st) {
-  const float inv_scale = (float)(1.0 / (double)p->softmax_scale);
   const int64_t nq = (int64_t)plan.Bq * plan.Hq * p->Sq, nk = (int64_t)plan.Bk * plan.Hk * p->Sk;
   pack_factor_kernel<T><<<(unsigned)((nq + 255) / 256), 256, 0, st>>>(
       reinterpret_cast<const T*>(p->q_bias), p->q_bias_stride[0], p->q_bias_stride[1], p->q_bias_stride[2], plan.Bq,
-      plan.Hq, p->Sq, p->R, plan.RP, plan.nsplit, inv_scale, 1, reinterpret_cast<T*>(qpack), nullptr, p->status);
+      plan.Hq, p->Sq, p->R, plan.RP, plan.qb_mult, reinterpret_cast<T*>(qpack), nullptr, p->status);
   pack_factor_kernel<T><<<(unsigned)((nk + 255) / 256), 256, 0, st>>>(
       reinterpret_cast<const T*>(p->k_bias), p->k_bias_stride[0], p->k_bias_stride[1], p->k_bias_stride[2], plan.Bk,
-      plan.Hk, p->Sk, p->R, plan.RP, plan.nsplit, 1.f, 0, reinterpret_cast<T*>(kpack), reinterpret_cast<T*>(kcenter),
-      p->status);
+      plan.Hk, p->Sk, p->R, plan.RP, 1.f, reinterpret_cast<T*>(kpack), reinterpret_cast<T*>(kcenter), p->status);
   note_launch(2);
   return (int)cudaGetLastError();
 }
@@ -111,6 +133,22 @@ int launch_pack(const fb_params* p, const PackPlan& plan, void* qpack, void* kpa
   if (plan.RP == 0) return 0;
   return p->dtype == FB_DTYPE_F16 ? launch_pack_t<__half>(p, plan, qpack, kpack, kcenter, st)
                                   : launch_pack_t<__nv_bfloat16>(p, plan, qpack, kpack, kcenter, st);
+}
+
+int launch_pack_qscaled(const fb_params* p, const PackPlan& plan, void* qs, cudaStream_t st) {
+  if (plan.nq == 1) return 0;
+  const int64_t n = (int64_t)p->B * p->H * p->Sq * (p->D / 8);
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  if (p->dtype == FB_DTYPE_F16)
+    pack_qscaled_kernel<__half><<<blocks, 256, 0, st>>>(reinterpret_cast<const __half*>(p->q), p->q_stride[0],
+                                                        p->q_stride[1], p->q_stride[2], p->B, p->H, p->Sq, p->D,
+                                                        p->softmax_scale, reinterpret_cast<__half*>(qs));
+  else
+    pack_qscaled_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(
+        reinterpret_cast<const __nv_bfloat16*>(p->q), p->q_stride[0], p->q_stride[1], p->q_stride[2], p->B, p->H,
+        p->Sq, p->D, p->softmax_scale, reinterpret_cast<__nv_bfloat16*>(qs));
+  note_launch();
+  return (int)cudaGetLastError();
 }
 
 }  // namespace fb
