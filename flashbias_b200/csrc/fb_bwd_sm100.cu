@@ -368,21 +368,28 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     float lse_raw, dlt;
     load_row_stats(0, lse_raw, dlt);
     float rsum_prev[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int it = 0; it < n_it; ++it) {
+    // One loop, one copy of each phase in the instruction stream: iteration `it` computes P/dS of query tile
+    // `it` and drains dQ of tile `it - 1` (after it when P/dS are double-buffered, before it otherwise).
+#pragma unroll 1
+    for (int it = 0; it <= n_it; ++it) {
+      if (!Cfg::PIPE && it > 0) drain(it - 1, rsum_prev);
+      if (it == n_it) {
+        if (Cfg::PIPE) drain(it - 1, rsum_prev);
+        break;
+      }
       const int q0 = (i_begin + it) * 128;
       const int grow = q0 + row;
       // a row that saw no key has lse = -inf: make its probabilities exactly zero
       const float lse2_cur = lse_raw == -INFINITY ? INFINITY : lse_raw * kLog2e, dlt_cur = dlt;
       load_row_stats(it + 1, lse_raw, dlt);  // next tile's statistics: the loads complete under this tile's math
-      if (!Cfg::PIPE && it > 0) drain(it - 1, rsum_prev);
       uint8_t* sP_gen = smem + Cfg::OFF_PDS + (Cfg::PIPE ? (it & 1) : 0) * Cfg::PDS_BYTES;
       uint8_t* sDS_gen = sP_gen + tile_bytes(128);
       const bool need_mask = (a.causal && k0 + 127 > q0) || (k0 + 128 > a.Sk);
-      float ds_sum[2];  // fp32 row sums of dS over this thread's two 32-column groups
+      float ds_sum0 = 0.f, ds_sum1 = 0.f;  // fp32 row sums of dS over this thread's two 32-column groups
       mbar_wait(s_full, it & 1, abort_flag, a.status);
       mbar_wait(dp_full, it & 1, abort_flag, a.status);
       tc_fence_after_sync();
-      uint32_t rs0[32], rd0[32], rs1[32], rd1[32];
+      uint32_t rs0[32], rd0[32];
       auto chunk = [&](uint32_t (&rs)[32], uint32_t (&rd)[32], int c) {
         const int col0 = wg * 64 + c * 32;
         float sum0 = 0.f, sum1 = 0.f;
@@ -398,7 +405,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           rs[i] = __float_as_uint(p);
           rd[i] = __float_as_uint(ds);
         }
-        ds_sum[c] = sum0 + sum1;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           uint4 wp, wd;
@@ -414,29 +420,29 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           *reinterpret_cast<uint4*>(sP_gen + off) = wp;
           *reinterpret_cast<uint4*>(sDS_gen + off) = wd;
         }
+        return sum0 + sum1;
       };
       const uint32_t tSl = tmem + Cfg::T_S + lane_off + wg * 64, tDl = tmem + Cfg::T_DP + lane_off + wg * 64;
-      tmem_ld32(tSl, rs0);
-      tmem_ld32(tDl, rd0);
-      tmem_wait_ld(rs0);
-      tmem_wait_ld(rd0);
-      tmem_ld32(tSl + 32, rs1);
-      tmem_ld32(tDl + 32, rd1);
-      chunk(rs0, rd0, 0);
-      tmem_wait_ld(rs1);
-      tmem_wait_ld(rd1);
-      chunk(rs1, rd1, 1);
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        tmem_ld32(tSl + c * 32, rs0);
+        tmem_ld32(tDl + c * 32, rd0);
+        tmem_wait_ld(rs0);
+        tmem_wait_ld(rd0);
+        const float sum = chunk(rs0, rd0, c);
+        if (c == 0) ds_sum0 = sum; else ds_sum1 = sum;
+      }
       // double-buffered by iteration parity: the named barrier of the next iteration orders reuse
       float* s_rowsum = reinterpret_cast<float*>(smem + Cfg::OFF_ROWSUM) + (it & 1) * 256;
       if (RP && wg == 0) {
-        s_rowsum[row] = ds_sum[0];
-        s_rowsum[128 + row] = ds_sum[1];
+        s_rowsum[row] = ds_sum0;
+        s_rowsum[128 + row] = ds_sum1;
       }
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(pds_ready);
       if (RP) asm volatile("bar.sync 1, 256;" ::: "memory");  // the two compute warpgroups only
-      float rsum[4] = {0.f, 0.f, ds_sum[0], ds_sum[1]};  // one per 32-key group of the tile
+      float rsum[4] = {0.f, 0.f, ds_sum0, ds_sum1};  // one per 32-key group of the tile
       if (RP && wg == 1) {
         rsum[0] = s_rowsum[row];
         rsum[1] = s_rowsum[128 + row];
@@ -445,7 +451,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
       for (int g = 0; g < 4; ++g) rsum_prev[g] = rsum[g];
     }
-    drain(n_it - 1, rsum_prev);
 
     // ---- epilogue: dV, dK (x scale), dKb (x scale, split terms folded)
     // the last dq_full phase covered every MMA of the CTA, so the accumulators are final
