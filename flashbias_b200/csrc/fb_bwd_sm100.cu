@@ -310,27 +310,35 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_wait(dq_full, it & 1, abort_flag, a.status);
       tc_fence_after_sync();
       {
-        float* dst = a.dq_acc + (((int64_t)b * a.Sq + grow) * a.H + h) * D + wg * DH;
-        if (DH == 16) {
+        // dQ tile: TMEM -> registers -> shared-memory staging ([128 rows][D floats], 16-byte chunks XOR-swizzled
+        // by row so the row-per-thread stores do not collide) -> reductions into the fp32 accumulator with 8
+        // consecutive lanes covering one 128-byte line of a row, instead of 32 lanes hitting 32 different rows.
+        // The staging area is the P tile of the buffer the MMAs of query tile `it` have finished reading.
+        uint8_t* stage = smem + Cfg::OFF_PDS + (Cfg::PIPE ? (it & 1) : 0) * Cfg::PDS_BYTES;
+        constexpr int CPR = D / 4;  // 16-byte chunks per row
+        auto stage_off = [&](int r, int ch) {
+          return (ch >> 3) * (128 * 128) + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
+        };
+#pragma unroll 1
+        for (int c0 = 0; c0 < DH; c0 += 16) {
           uint32_t r[16];
-          tmem_ld16(tmem + Cfg::T_DQ + lane_off + wg * DH, r);
+          tmem_ld16(tmem + Cfg::T_DQ + lane_off + wg * DH + c0, r);
           tmem_wait_ld(r);
-          if (grow < a.Sq) {
 #pragma unroll
-            for (int g = 0; g < 4; ++g)
-              red_add_v4(dst + g * 4, __uint_as_float(r[g * 4]), __uint_as_float(r[g * 4 + 1]),
-                         __uint_as_float(r[g * 4 + 2]), __uint_as_float(r[g * 4 + 3]));
-          }
-        } else {
-          uint32_t r[32];
-          tmem_ld32(tmem + Cfg::T_DQ + lane_off + wg * DH, r);
-          tmem_wait_ld(r);
-          if (grow < a.Sq) {
+          for (int g = 0; g < 4; ++g)
+            *reinterpret_cast<uint4*>(stage + stage_off(row, (wg * DH + c0) / 4 + g)) =
+                make_uint4(r[g * 4], r[g * 4 + 1], r[g * 4 + 2], r[g * 4 + 3]);
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        const int q0d = (i_begin + it) * 128;
+        const int tid = warp * 32 + lane;  // 0..255
 #pragma unroll
-            for (int g = 0; g < 8; ++g)
-              red_add_v4(dst + g * 4, __uint_as_float(r[g * 4]), __uint_as_float(r[g * 4 + 1]),
-                         __uint_as_float(r[g * 4 + 2]), __uint_as_float(r[g * 4 + 3]));
-          }
+        for (int i = 0; i < (128 * CPR) / 256; ++i) {
+          const int cid = i * 256 + tid;
+          const int rr = cid / CPR, ch = cid % CPR;
+          const float4 v = *reinterpret_cast<const float4*>(stage + stage_off(rr, ch));
+          if (q0d + rr < a.Sq)
+            red_add_v4(a.dq_acc + (((int64_t)b * a.Sq + q0d + rr) * a.H + h) * D + ch * 4, v.x, v.y, v.z, v.w);
         }
       }
       if (RP && wg == 1) {
