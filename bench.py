@@ -51,6 +51,10 @@ CPU_SAMPLE = {
 }
 
 
+# DRAM bytes (read + write) per launch of the backward main kernel, measured with ncu on this workload
+NCU_BWD_TRAFFIC_BYTES = {"alibi": 1188577536 + 429711104}
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -308,7 +312,11 @@ def main():
             "roofline": {"bound": "tensor", "kernel": "bwd_sm100_kernel", "achieved": ach,
                          "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                          "frac": (ach / peaks["bf16_tflops"]) if ach else None, "peak_source": peaks["source"],
-                         "ms_per_launch": bwd_kernel_ms, "launches_timed": kn.value, "traffic": None},
+                         "ms_per_launch": bwd_kernel_ms, "launches_timed": kn.value,
+                         "flop_per_launch": fl_b,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel, from the ncu
+                         # capture summarised in profiles/bench_alibi_launch_list.md (full-size alibi workload)
+                         "traffic": NCU_BWD_TRAFFIC_BYTES.get(args.workload)},
         }
         if not args.no_cpu_baseline and world == 1:
             from oracle import flashbias_oracle as orc

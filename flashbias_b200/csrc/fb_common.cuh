@@ -104,7 +104,7 @@ __device__ __forceinline__ void tc_fence_after_sync() {
 }
 
 // ---------------------------------------------------------------------------------------------
-// TMA: tiled bulk tensor load, global -> shared, completion on an mbarrier.  No multicast.
+// TMA: tiled bulk tensor load, global -> shared, completion on an mbarrier.  Every CTA loads its own copy.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
