@@ -56,7 +56,7 @@ struct BwdCfg {
   // P and dS tiles are double-buffered when shared memory allows it, so that the exponentials of
   // query tile i+1 overlap the dV/dK/dQ MMAs of query tile i.
   static constexpr bool PIPE =
-      (D == 32) && (2 * D_BYTES + 2 * R_BYTES + 2 * STAGE_BYTES + 2 * PDS_BYTES + 8192 <= 227 * 1024);
+      (D == 32) && (2 * D_BYTES + 2 * R_BYTES + 2 * STAGE_BYTES + 2 * PDS_BYTES + 12288 <= 227 * 1024);
   static constexpr int NBUF = PIPE ? 2 : 1;
   // [Q|Qb] and [K|Kc] read as one MN-major operand of N = D + RP (two 64-byte-swizzled tiles)
   static constexpr bool MERGE = (D == 32 && RP == 32);
@@ -67,8 +67,8 @@ struct BwdCfg {
   static constexpr int OFF_STAGE = OFF_V + D_BYTES;
   static constexpr int OFF_PDS = OFF_STAGE + 2 * STAGE_BYTES;
   static constexpr int OFF_BAR = OFF_PDS + NBUF * PDS_BYTES;
-  static constexpr int OFF_ROWSUM = OFF_BAR + 256;       // 2 x 2 x 128 floats: dS row sums of warpgroup 0
-  static constexpr int OFF_KBC = OFF_ROWSUM + 2048;      // 4 x RPX floats: k_bias of the 4 centre keys
+  static constexpr int OFF_ROWSUM = OFF_BAR + 256;       // 4 x 4 x 128 floats: dS row sums per 32-key group
+  static constexpr int OFF_KBC = OFF_ROWSUM + 8192;      // 4 x RPX floats: k_bias of the 4 centre keys
   static constexpr int SMEM = OFF_KBC + 4 * RPX * 4 + 1024;
   // tensor-memory columns
   static constexpr int T_S = 0, T_DP = 128, T_DV = 256, T_DK = T_DV + D, T_DKB = T_DK + D, T_DQ = T_DKB + RP,
@@ -92,7 +92,7 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 }
 
 template <typename T, int D, int RP, int NQ>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(448, 1)
 bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                  const __grid_constant__ CUtensorMap tmQb, const __grid_constant__ CUtensorMap tmKb,
@@ -109,7 +109,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                  sStage = sbase + Cfg::OFF_STAGE, sPDS = sbase + Cfg::OFF_PDS;
   const uint32_t bar0 = sbase + Cfg::OFF_BAR;
   const uint32_t kv_full = bar0, s_full = bar0 + 8, dp_full = bar0 + 16, pds_ready = bar0 + 24,
-                 dq_full = bar0 + 32, dq_drained = bar0 + 40, qdo_full = bar0 + 48 /*2*/, qdo_free = bar0 + 64 /*2*/;
+                 dq_full = bar0 + 32, dq_drained = bar0 + 40, qdo_full = bar0 + 48 /*2*/, qdo_free = bar0 + 64 /*2*/,
+                 pds_free = bar0 + 80 /*2*/, all_done = bar0 + 112;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::OFF_BAR + 96);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::OFF_BAR + 104);
 
@@ -128,7 +129,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int i_begin = a.causal ? kt : 0;  // first query tile with a row >= k0
   const int n_it = a.nq_tiles - i_begin;  // may be <= 0 when Sq < Sk under causal masking
 
-  if (warp == 9) {
+  if (warp == 13) {
     if (lane == 0) {
       *abort_flag = 0;
       mbar_init(kv_full, 1);
@@ -136,10 +137,12 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(dp_full, 1);
       mbar_init(pds_ready, 256);
       mbar_init(dq_full, 1);
-      mbar_init(dq_drained, 256);
+      mbar_init(dq_drained, 128);  // the drain warpgroup
+      mbar_init(all_done, 1);
       for (int i = 0; i < 2; ++i) {
         mbar_init(qdo_full + 8 * i, 1);
         mbar_init(qdo_free + 8 * i, 1);
+        mbar_init(pds_free + 8 * i, 1);
       }
       mbar_fence_init();
     }
@@ -152,7 +155,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp == 8) {
+  if (warp == 12) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0 && n_it > 0) {
       const int hq = a.hq_bcast ? 0 : h, bq = a.bq_bcast ? 0 : b;
@@ -174,7 +177,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (NQ == 2) tma_tile_bwd<D>(base + Cfg::OFF_QLO, &tmQ, qdo_full + 8 * st, q0, h, b, D);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == 13) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && n_it > 0) {
       constexpr uint32_t idS = instr_desc(kBf16, false, false, 128, 128);  // S, dP: both operands K-major
@@ -271,25 +274,89 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         umma_commit(dq_full);
         umma_commit(qdo_free + 8 * st);
+        umma_commit(pds_free + 8 * (Cfg::PIPE ? st : 0));  // P/dS buffer of this tile may be rewritten
         if (!Cfg::PIPE && it + 1 < n_it) issue_S_dP(it + 1);
+      }
+      umma_commit(all_done);  // every MMA of the CTA
+    }
+  } else if (warp >= 8 && warp < 12) {
+    // ------------------------------------------------------------------ drain warpgroup
+    // dQ | dQb of each query tile from TMEM into the fp32 accumulators in global memory, off the critical path
+    // of the warps that compute P and dS.  One thread per query row.
+    if (n_it > 0) {
+      const int row = (warp & 3) * 32 + lane;
+      const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+      const float* s_kbc = reinterpret_cast<const float*>(smem + Cfg::OFF_KBC);
+#pragma unroll 1
+      for (int it = 0; it < n_it; ++it) {
+        const int grow = (i_begin + it) * 128 + row;
+        mbar_wait(dq_full, it & 1, abort_flag, a.status);
+        tc_fence_after_sync();
+        float* dst = a.dq_acc + (((int64_t)b * a.Sq + grow) * a.H + h) * D;
+#pragma unroll 1
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld32(tmem + Cfg::T_DQ + lane_off + c0, r);
+          tmem_wait_ld(r);
+          if (grow < a.Sq) {
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+              red_add_v4(dst + c0 + g * 4, __uint_as_float(r[g * 4]), __uint_as_float(r[g * 4 + 1]),
+                         __uint_as_float(r[g * 4 + 2]), __uint_as_float(r[g * 4 + 3]));
+          }
+        }
+        if (RP) {
+          // dq_bias = dS . k_bias, evaluated per group of 32 keys as dS16 . (k_bias - c) + c * rowsum_fp32(dS)
+          // with c the k_bias of the group's middle key: rows of dS sum to ~0, so rounding dS to 16 bits
+          // against a large, slowly varying factor (ALiBi positions) would otherwise dominate the result.
+          const float* s_rowsum = reinterpret_cast<const float*>(smem + Cfg::OFF_ROWSUM) + (it & 3) * 512;
+          float rsum[4];
+#pragma unroll
+          for (int g = 0; g < 4; ++g) rsum[g] = s_rowsum[g * 128 + row];
+          const int bq = a.bq_bcast ? 0 : b, hq = a.hq_bcast ? 0 : h;
+          float* dstb = a.dqb_acc + (((int64_t)bq * a.Sq + grow) * a.Hq + hq) * a.R;
+          const int used = 2 * a.R;  // (hi, lo) column groups of the centred factor
+#pragma unroll 1
+          for (int c0 = 0; c0 < RPX && c0 < used; c0 += 16) {
+            uint32_t r[16];
+            tmem_ld16(tmem + Cfg::T_DQB + lane_off + c0, r);
+            tmem_wait_ld(r);
+            if (grow < a.Sq) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                const int c = c0 + i;
+                if (c < a.R) {
+                  float v = __uint_as_float(r[i]);
+#pragma unroll
+                  for (int g = 0; g < 4; ++g) v = fmaf(s_kbc[g * RPX + c], rsum[g], v);
+                  atomicAdd(dstb + c, v);
+                } else if (c < used) {
+                  atomicAdd(dstb + c - a.R, __uint_as_float(r[i]));
+                }
+              }
+            }
+          }
+        }
+        tc_fence_before_sync();
+        mbar_arrive(dq_drained);
       }
     }
   } else if (n_it > 0) {
-    // ------------------------------------------------------------------ compute warpgroups
+    // ------------------------------------------------------------------ compute warpgroups (warps 0-7)
     const int wg = warp >> 2;
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     const float sl2 = a.scale_log2;
-    constexpr int DH = D / 2;  // dQ columns per warpgroup
+    constexpr int DH = D / 2;  // dV / dK columns per warpgroup in the epilogue
     float* s_kbc = reinterpret_cast<float*>(smem + Cfg::OFF_KBC);
     if (RP) {
-      // k_bias of the four keys the centred copy refers to (one per 32-key group), as fp32
+      // k_bias of the four keys the centred copy refers to (one per 32-key group), as fp32; read by the drain
+      // warpgroup, which is ordered after this through the first pds_ready -> dq_full chain
       const T* kb_bh = a.k_bias_t<T>() + (a.bk_bcast ? 0 : b) * a.kb_stride[0] + (a.hk_bcast ? 0 : h) * a.kb_stride[1];
       for (int i = threadIdx.x; i < 4 * RPX; i += 256) {
         const int g = i / RPX, c = i % RPX;
         s_kbc[i] = c < a.R ? to_f32(kb_bh[(int64_t)min(k0 + 32 * g + 16, a.Sk - 1) * a.kb_stride[2] + c]) : 0.f;
       }
-      asm volatile("bar.sync 1, 256;" ::: "memory");
     }
 
     // Raw loads only: the values are consumed one iteration later, so the global-memory latency
@@ -304,87 +371,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     };
 
-    // dQ | dQb of query tile `it` from TMEM into the fp32 accumulators in global memory
-    auto drain = [&](int it, const float (&rsum)[4]) {
-      const int grow = (i_begin + it) * 128 + row;
-      mbar_wait(dq_full, it & 1, abort_flag, a.status);
-      tc_fence_after_sync();
-      {
-        // dQ tile: TMEM -> registers -> shared-memory staging ([128 rows][D floats], 16-byte chunks XOR-swizzled
-        // by row so the row-per-thread stores do not collide) -> reductions into the fp32 accumulator with 8
-        // consecutive lanes covering one 128-byte line of a row, instead of 32 lanes hitting 32 different rows.
-        // The staging area is the P tile of the buffer the MMAs of query tile `it` have finished reading.
-        uint8_t* stage = smem + Cfg::OFF_PDS + (Cfg::PIPE ? (it & 1) : 0) * Cfg::PDS_BYTES;
-        constexpr int CPR = D / 4;  // 16-byte chunks per row
-        auto stage_off = [&](int r, int ch) {
-          return (ch >> 3) * (128 * 128) + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
-        };
-#pragma unroll 1
-        for (int c0 = 0; c0 < DH; c0 += 16) {
-          uint32_t r[16];
-          tmem_ld16(tmem + Cfg::T_DQ + lane_off + wg * DH + c0, r);
-          tmem_wait_ld(r);
-#pragma unroll
-          for (int g = 0; g < 4; ++g)
-            *reinterpret_cast<uint4*>(stage + stage_off(row, (wg * DH + c0) / 4 + g)) =
-                make_uint4(r[g * 4], r[g * 4 + 1], r[g * 4 + 2], r[g * 4 + 3]);
-        }
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        const int q0d = (i_begin + it) * 128;
-        const int tid = warp * 32 + lane;  // 0..255
-#pragma unroll
-        for (int i = 0; i < (128 * CPR) / 256; ++i) {
-          const int cid = i * 256 + tid;
-          const int rr = cid / CPR, ch = cid % CPR;
-          const float4 v = *reinterpret_cast<const float4*>(stage + stage_off(rr, ch));
-          if (q0d + rr < a.Sq)
-            red_add_v4(a.dq_acc + (((int64_t)b * a.Sq + q0d + rr) * a.H + h) * D + ch * 4, v.x, v.y, v.z, v.w);
-        }
-      }
-      if (RP && wg == 1) {
-        // dq_bias = dS . k_bias, evaluated per group of 32 keys as dS16 . (k_bias - c) + c * rowsum_fp32(dS)
-        // with c the k_bias of the group's middle key: rows of dS sum to ~0, so rounding dS to 16 bits
-        // against a large, slowly varying factor (ALiBi positions) would otherwise dominate the result.
-        const int bq = a.bq_bcast ? 0 : b, hq = a.hq_bcast ? 0 : h;
-        float* dst = a.dqb_acc + (((int64_t)bq * a.Sq + grow) * a.Hq + hq) * a.R;
-        const int used = 2 * a.R;  // (hi, lo) column groups of the centred factor
-#pragma unroll 1
-        for (int c0 = 0; c0 < RPX && c0 < used; c0 += 16) {
-          uint32_t r[16];
-          tmem_ld16(tmem + Cfg::T_DQB + lane_off + c0, r);
-          tmem_wait_ld(r);
-          if (grow < a.Sq) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const int c = c0 + i;
-              if (c < a.R) {
-                float v = __uint_as_float(r[i]);
-#pragma unroll
-                for (int g = 0; g < 4; ++g) v = fmaf(s_kbc[g * RPX + c], rsum[g], v);
-                atomicAdd(dst + c, v);
-              } else if (c < used) {
-                atomicAdd(dst + c - a.R, __uint_as_float(r[i]));
-              }
-            }
-          }
-        }
-      }
-      tc_fence_before_sync();
-      mbar_arrive(dq_drained);
-    };
-
     float lse_raw, dlt;
     load_row_stats(0, lse_raw, dlt);
-    float rsum_prev[4] = {0.f, 0.f, 0.f, 0.f};
-    // One loop, one copy of each phase in the instruction stream: iteration `it` computes P/dS of query tile
-    // `it` and drains dQ of tile `it - 1` (after it when P/dS are double-buffered, before it otherwise).
 #pragma unroll 1
-    for (int it = 0; it <= n_it; ++it) {
-      if (!Cfg::PIPE && it > 0) drain(it - 1, rsum_prev);
-      if (it == n_it) {
-        if (Cfg::PIPE) drain(it - 1, rsum_prev);
-        break;
-      }
+    for (int it = 0; it < n_it; ++it) {
       const int q0 = (i_begin + it) * 128;
       const int grow = q0 + row;
       // a row that saw no key has lse = -inf: make its probabilities exactly zero
@@ -396,6 +386,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       float ds_sum0 = 0.f, ds_sum1 = 0.f;  // fp32 row sums of dS over this thread's two 32-column groups
       mbar_wait(s_full, it & 1, abort_flag, a.status);
       mbar_wait(dp_full, it & 1, abort_flag, a.status);
+      // the MMAs that read this P/dS buffer last (query tile it - NBUF) have completed
+      if (it >= Cfg::NBUF) {
+        if (Cfg::PIPE) mbar_wait(pds_free + 8 * (it & 1), ((it >> 1) - 1) & 1, abort_flag, a.status);
+        else mbar_wait(pds_free, (it - 1) & 1, abort_flag, a.status);
+      }
       tc_fence_after_sync();
       uint32_t rs0[32], rd0[32];
       auto chunk = [&](uint32_t (&rs)[32], uint32_t (&rd)[32], int c) {
@@ -440,25 +435,19 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const float sum = chunk(rs0, rd0, c);
         if (c == 0) ds_sum0 = sum; else ds_sum1 = sum;
       }
-      // double-buffered by iteration parity: the named barrier of the next iteration orders reuse
-      float* s_rowsum = reinterpret_cast<float*>(smem + Cfg::OFF_ROWSUM) + (it & 1) * 256;
-      if (RP && wg == 0) {
-        s_rowsum[row] = ds_sum0;
-        s_rowsum[128 + row] = ds_sum1;
+      if (RP) {
+        // four buffers: the drain warpgroup may lag up to three query tiles behind
+        float* s_rowsum = reinterpret_cast<float*>(smem + Cfg::OFF_ROWSUM) + (it & 3) * 512;
+        s_rowsum[(2 * wg) * 128 + row] = ds_sum0;
+        s_rowsum[(2 * wg + 1) * 128 + row] = ds_sum1;
       }
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(pds_ready);
-      if (RP) asm volatile("bar.sync 1, 256;" ::: "memory");  // the two compute warpgroups only
-      float rsum[4] = {0.f, 0.f, ds_sum0, ds_sum1};  // one per 32-key group of the tile
-      if (RP && wg == 1) {
-        rsum[0] = s_rowsum[row];
-        rsum[1] = s_rowsum[128 + row];
-      }
-      if (Cfg::PIPE && it > 0) drain(it - 1, rsum_prev);
-#pragma unroll
-      for (int g = 0; g < 4; ++g) rsum_prev[g] = rsum[g];
     }
+    // the dV and dK|dKb accumulators are final once every MMA of the CTA has completed
+    mbar_wait(all_done, 0, abort_flag, a.status);
+    tc_fence_after_sync();
 
     // ---- epilogue: dV, dK (x scale), dKb (x scale, split terms folded)
     // the last dq_full phase covered every MMA of the CTA, so the accumulators are final
@@ -524,7 +513,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == 13) {
     __syncwarp();
     tmem_dealloc(tmem, 512);
   }
@@ -693,7 +682,7 @@ static int launch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t s
   }
   const unsigned grid = (unsigned)((int64_t)a.nk_tiles * p->B * p->H);
   prof_before(KC_BWD_MAIN, st);
-  kern<<<grid, 320, Cfg::SMEM, st>>>(tQ, tK, tV, tDO, tQb, tKb, tKc, a);
+  kern<<<grid, 448, Cfg::SMEM, st>>>(tQ, tK, tV, tDO, tQb, tKb, tKc, a);
   prof_after(KC_BWD_MAIN, st);
   note_launch();
   if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
