@@ -110,7 +110,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const uint32_t bar0 = sbase + Cfg::OFF_BAR;
   const uint32_t kv_full = bar0, s_full = bar0 + 8, dp_full = bar0 + 16, pds_ready = bar0 + 24,
                  dq_full = bar0 + 32, dq_drained = bar0 + 40, qdo_full = bar0 + 48 /*2*/, qdo_free = bar0 + 64 /*2*/,
-                 pds_free = bar0 + 80 /*2*/, all_done = bar0 + 112;
+                 pds_free = bar0 + 80 /*2*/, all_done = bar0 + 112, stg_free = bar0 + 120 /*2*/;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::OFF_BAR + 96);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::OFF_BAR + 104);
 
@@ -143,6 +143,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         mbar_init(qdo_full + 8 * i, 1);
         mbar_init(qdo_free + 8 * i, 1);
         mbar_init(pds_free + 8 * i, 1);
+        mbar_init(stg_free + 8 * i, 4);  // one arrival per drain warp
       }
       mbar_fence_init();
     }
@@ -292,18 +293,55 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const int grow = (i_begin + it) * 128 + row;
         mbar_wait(dq_full, it & 1, abort_flag, a.status);
         tc_fence_after_sync();
-        float* dst = a.dq_acc + (((int64_t)b * a.Sq + grow) * a.H + h) * D;
+        if (!Cfg::PIPE) {
+          // single P/dS buffer: no spare tile to stage in, reduce straight from registers (one row per thread)
+          float* dst = a.dq_acc + (((int64_t)b * a.Sq + grow) * a.H + h) * D;
 #pragma unroll 1
-        for (int c0 = 0; c0 < D; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld32(tmem + Cfg::T_DQ + lane_off + c0, r);
-          tmem_wait_ld(r);
-          if (grow < a.Sq) {
+          for (int c0 = 0; c0 < D; c0 += 32) {
+            uint32_t r[32];
+            tmem_ld32(tmem + Cfg::T_DQ + lane_off + c0, r);
+            tmem_wait_ld(r);
+            if (grow < a.Sq) {
 #pragma unroll
-            for (int g = 0; g < 8; ++g)
-              red_add_v4(dst + c0 + g * 4, __uint_as_float(r[g * 4]), __uint_as_float(r[g * 4 + 1]),
-                         __uint_as_float(r[g * 4 + 2]), __uint_as_float(r[g * 4 + 3]));
+              for (int g = 0; g < 8; ++g)
+                red_add_v4(dst + c0 + g * 4, __uint_as_float(r[g * 4]), __uint_as_float(r[g * 4 + 1]),
+                           __uint_as_float(r[g * 4 + 2]), __uint_as_float(r[g * 4 + 3]));
+            }
           }
+        } else {
+          // dQ tile: TMEM -> registers -> shared-memory staging ([128 rows][D floats], 16-byte chunks XOR-swizzled
+          // by row) -> vector reductions with 8 consecutive lanes covering one 128-byte line of a row.  Row-per-
+          // thread reductions would put 32 different lines into every instruction and crowd the load/store unit
+          // that the compute warps need for their P/dS stores.  The staging area is the P tile of the buffer the
+          // MMAs of this query tile have finished reading; it is handed back through stg_free.
+          const int buf = Cfg::PIPE ? (it & 1) : 0;
+          uint8_t* stage = smem + Cfg::OFF_PDS + buf * Cfg::PDS_BYTES;
+          constexpr int CPR = D / 4;  // 16-byte chunks per row
+          auto stage_off = [&](int r, int ch) {
+            return (ch >> 3) * (128 * 128) + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
+          };
+#pragma unroll 1
+          for (int c0 = 0; c0 < D; c0 += 16) {
+            uint32_t r[16];
+            tmem_ld16(tmem + Cfg::T_DQ + lane_off + c0, r);
+            tmem_wait_ld(r);
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+              *reinterpret_cast<uint4*>(stage + stage_off(row, c0 / 4 + g)) =
+                  make_uint4(r[g * 4], r[g * 4 + 1], r[g * 4 + 2], r[g * 4 + 3]);
+          }
+          asm volatile("bar.sync 3, 128;" ::: "memory");  // the drain warpgroup only
+          const int q0d = (i_begin + it) * 128;
+          const int tid = (warp & 3) * 32 + lane;  // 0..127
+#pragma unroll 1
+          for (int i = 0; i < (128 * CPR) / 128; ++i) {
+            const int cid = i * 128 + tid;
+            const int rr = cid / CPR, ch = cid % CPR;
+            const float4 v = *reinterpret_cast<const float4*>(stage + stage_off(rr, ch));
+            if (q0d + rr < a.Sq)
+              red_add_v4(a.dq_acc + (((int64_t)b * a.Sq + q0d + rr) * a.H + h) * D + ch * 4, v.x, v.y, v.z, v.w);
+          }
+          mbar_arrive_warp(stg_free + 8 * buf);  // staging reads done: the P tile may be rewritten
         }
         if (RP) {
           // dq_bias = dS . k_bias, evaluated per group of 32 keys as dS16 . (k_bias - c) + c * rowsum_fp32(dS)
@@ -388,8 +426,12 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_wait(dp_full, it & 1, abort_flag, a.status);
       // the MMAs that read this P/dS buffer last (query tile it - NBUF) have completed
       if (it >= Cfg::NBUF) {
-        if (Cfg::PIPE) mbar_wait(pds_free + 8 * (it & 1), ((it >> 1) - 1) & 1, abort_flag, a.status);
-        else mbar_wait(pds_free, (it - 1) & 1, abort_flag, a.status);
+        if (Cfg::PIPE) {
+          mbar_wait(pds_free + 8 * (it & 1), ((it >> 1) - 1) & 1, abort_flag, a.status);
+          mbar_wait(stg_free + 8 * (it & 1), ((it >> 1) - 1) & 1, abort_flag, a.status);
+        } else {
+          mbar_wait(pds_free, (it - 1) & 1, abort_flag, a.status);
+        }
       }
       tc_fence_after_sync();
       uint32_t rs0[32], rd0[32];
