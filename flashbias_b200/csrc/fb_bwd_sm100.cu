@@ -3,18 +3,21 @@
 // One CTA owns one tile of 128 keys of one (batch, head): K|packed k_bias and V stay resident in
 // shared memory, the dK|dk_bias and dV accumulators stay resident in tensor memory (no atomics on
 // them), and the CTA walks the query tiles that see those keys:
-//   warp 8      TMA producer: K|Kb, V once; then Q|Qb and dO tiles through a 2-stage ring.
-//   warp 9      MMA issuer (one thread), per query tile:
-//                 S  = [Q|Qb].[K|Kb]^T          dP = dO.V^T                     (TMEM, fresh)
-//                 dV += P^T.dO                  dK|dKb += dS^T.[Q|Qb]           (TMEM, accumulated)
-//                 dQ|dQb = dS.[K|Kb]                                            (TMEM, fresh)
+//   warp 12     TMA producer: K|Kb|Kc, V once; then Q|Qb and dO tiles through a 2-stage ring.
+//   warps 13-16 MMA issuers (one thread each, one per warp scheduler), per query tile:
+//                 13: S  = [Q|Qb].[K|Kb]^T      dP = dO.V^T                     (TMEM, fresh)
+//                 14: dV += P^T.dO              15: dK|dKb += dS^T.[Q|Qb]       (TMEM, accumulated)
+//                 16: dQ|dQb = dS.[K|Kc]                                        (TMEM, fresh)
 //   warps 0-7   two warpgroups, each thread owns one query row (TMEM lane) and half of the key
 //               columns: P = exp2(S*scale*log2e - lse*log2e), dS = P*(dP - delta), both rounded to
-//               16 bits and written to shared memory as operand tiles; then the dQ|dQb tile is read
-//               from TMEM and added to fp32 accumulators in global memory with vector reductions.
+//               16 bits and written to shared memory as operand tiles.
+//   warps 8-11  drain warpgroup: the dQ|dQb tile is read from TMEM and added to fp32 accumulators in
+//               global memory with vector reductions.
 // dQ is the only quantity that crosses CTAs (every key tile contributes to every query row), hence
 // the fp32 accumulators; a final pass scales and rounds them.  P and dS are read by the tensor core
 // both "as stored" and transposed, which is only a different shared-memory descriptor.
+#include <stdlib.h>
+
 #include <type_traits>
 
 #include "fb_common.cuh"
@@ -40,6 +43,7 @@ struct BwdArgs {
   const void* k_bias;  // original (unpacked) k-side factor and its (batch, head, row) strides
   int64_t kb_stride[3];
   int* status;
+  int dbg;  // development toggles, honoured only in -DFB_TRACE builds
   template <typename T>
   __device__ __forceinline__ const T* k_bias_t() const { return reinterpret_cast<const T*>(k_bias); }
 };
@@ -74,6 +78,10 @@ struct BwdCfg {
   static constexpr int T_S = 0, T_DP = 128, T_DV = 256, T_DK = T_DV + D, T_DKB = T_DK + D, T_DQ = T_DKB + RP,
                        T_DQB = T_DQ + D, T_END = T_DQB + RP;
   static_assert(T_END <= 512, "tensor memory budget exceeded");
+  // a second dQ|dQb accumulator when tensor memory has room: the dQ MMAs of query tile i+1 then do not wait
+  // for the drain of tile i
+  static constexpr int NDQ = (T_END + D + RP <= 512) ? 2 : 1;
+  static constexpr int DQ_STRIDE = T_END - T_DQ;  // columns between the two accumulators
   static constexpr bool FITS = SMEM <= 227 * 1024;  // otherwise the variant is not built (shape-generic kernels)
 };
 
@@ -91,8 +99,39 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
                : "memory");
 }
 
+// Development aid, compiled only with -DFB_TRACE: CTA 0 records clock64() at the phase boundaries of each
+// warp role, 16 slots per query tile.
+#ifdef FB_TRACE
+__device__ long long g_bwd_trace[64 * 32];
+#define FB_TRACE_MARK(it, slot) \
+  do { if (blockIdx.x == 0 && (it) < 64) g_bwd_trace[(it) * 32 + (slot)] = clock64(); } while (0)
+#define FB_DBG(bit) ((a.dbg & (bit)) != 0)
+#else
+#define FB_TRACE_MARK(it, slot) do { } while (0)
+#define FB_DBG(bit) false
+#endif
+
+// Bulk asynchronous reduction shared -> global (fp32 add), executed by the copy engine instead of the
+// load/store unit.  Both addresses 16-byte aligned, size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_reduce_add_f32(float* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(dst), "r"(src_smem),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the shared-memory source of every committed group has been read
+__device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// Byte offset of 16-byte chunk `ch` of row `r` in a staged [128][D] fp32 dQ tile: 128-byte lines, chunks XOR-swizzled
+// by row so that one row per thread writes without bank conflicts.  The fp32 dQ accumulator in global memory keeps
+// this arrangement per (batch, head, query tile) when the tile is reduced in bulk.
+__host__ __device__ __forceinline__ int dq_stage_off(int r, int ch) {
+  return (ch >> 3) * (128 * 128) + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
+}
+
 template <typename T, int D, int RP, int NQ>
-__global__ void __launch_bounds__(448, 1)
+__global__ void __launch_bounds__(544, 1)
 bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                  const __grid_constant__ CUtensorMap tmQb, const __grid_constant__ CUtensorMap tmKb,
@@ -108,8 +147,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const uint32_t sK = sbase + Cfg::OFF_K, sKb = sbase + Cfg::OFF_KB, sKc = sbase + Cfg::OFF_KC, sV = sbase + Cfg::OFF_V,
                  sStage = sbase + Cfg::OFF_STAGE, sPDS = sbase + Cfg::OFF_PDS;
   const uint32_t bar0 = sbase + Cfg::OFF_BAR;
-  const uint32_t kv_full = bar0, s_full = bar0 + 8, dp_full = bar0 + 16, pds_ready = bar0 + 24,
-                 dq_full = bar0 + 32, dq_drained = bar0 + 40, qdo_full = bar0 + 48 /*2*/, qdo_free = bar0 + 64 /*2*/,
+  const uint32_t kv_full = bar0, s_full = bar0 + 8, dp_full = bar0 + 16, pds_ready = bar0 + 136 /*2*/,
+                 dq_full = bar0 + 32 /*2*/, dq_drained = bar0 + 152 /*2*/, sdp_read = bar0 + 24, qdo_full = bar0 + 48 /*2*/, qdo_free = bar0 + 64 /*2*/,
                  pds_free = bar0 + 80 /*2*/, all_done = bar0 + 112, stg_free = bar0 + 120 /*2*/;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::OFF_BAR + 96);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::OFF_BAR + 104);
@@ -135,15 +174,16 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(kv_full, 1);
       mbar_init(s_full, 1);
       mbar_init(dp_full, 1);
-      mbar_init(pds_ready, 256);
-      mbar_init(dq_full, 1);
-      mbar_init(dq_drained, 128);  // the drain warpgroup
-      mbar_init(all_done, 1);
+      mbar_init(sdp_read, 8);  // every compute warp has S and dP of the tile in registers
+      mbar_init(all_done, 4);  // one commit per issuing thread
       for (int i = 0; i < 2; ++i) {
         mbar_init(qdo_full + 8 * i, 1);
-        mbar_init(qdo_free + 8 * i, 1);
-        mbar_init(pds_free + 8 * i, 1);
-        mbar_init(stg_free + 8 * i, 4);  // one arrival per drain warp
+        mbar_init(qdo_free + 8 * i, 3);  // S|dP, dV and dK chains read a stage
+        mbar_init(pds_free + 8 * i, 3);  // dV, dK and dQ chains read a P/dS buffer
+        mbar_init(dq_full + 8 * i, 1);
+        mbar_init(dq_drained + 8 * i, 4);  // the drain warps
+        mbar_init(pds_ready + 8 * i, 8);   // the compute warps  // alternating by query tile: the four issuers wait at different times
+        mbar_init(stg_free + 8 * i, 1);  // the drain thread that issued the bulk reduction
       }
       mbar_fence_init();
     }
@@ -178,107 +218,144 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (NQ == 2) tma_tile_bwd<D>(base + Cfg::OFF_QLO, &tmQ, qdo_full + 8 * st, q0, h, b, D);
       }
     }
-  } else if (warp == 13) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp >= 13) {
+    // ------------------------------------------------------------------ MMA issuers
+    // Four warps, one elected thread each, one per warp scheduler.  A thread that issues tcgen05.mma gets an
+    // issue slot only when the compute warps of its scheduler stall, so one thread alone cannot feed the tensor
+    // core; the chains below are independent (different accumulators) and run concurrently:
+    //   role 0  S and dP of the next query tile      role 1  dV (and dKb when it is a separate accumulator)
+    //   role 2  dK (or dK|dKb merged)                role 3  dQ | dQb
+    // Every accumulator is only ever touched by one thread, which keeps its MMAs ordered.
     if (lane == 0 && n_it > 0) {
+      const int role = warp - 13;
       constexpr uint32_t idS = instr_desc(kBf16, false, false, 128, 128);  // S, dP: both operands K-major
       constexpr uint32_t idTD = instr_desc(kBf16, true, true, 128, D);     // dV, dK: A^T (MN-major), B MN-major
       constexpr uint32_t idTR = instr_desc(kBf16, true, true, 128, RPX);   // dKb
       constexpr uint32_t idQD = instr_desc(kBf16, false, true, 128, D);    // dQ: A K-major, B MN-major
       constexpr uint32_t idQR = instr_desc(kBf16, false, true, 128, RPX);  // dQb
-      // descriptor views built once (stage 0 / buffer 0); each MMA adds a constant to the address field
-      const DescBase kQ = kmajor_base<D>(sStage), kDO = kmajor_base<D>(sStage + Cfg::D_BYTES),
-                     kQb = kmajor_base<RPX>(sStage + 2 * Cfg::D_BYTES), kK = kmajor_base<D>(sK),
-                     kKb = kmajor_base<RPX>(sKb), kV = kmajor_base<D>(sV);
-      const DescBase mQ = mnmajor_base<D>(sStage), mDO = mnmajor_base<D>(sStage + Cfg::D_BYTES),
-                     mQb = mnmajor_base<RPX>(sStage + 2 * Cfg::D_BYTES), mK = mnmajor_base<D>(sK),
-                     mKc = mnmajor_base<RPX>(sKc), mP = mnmajor_base<128>(sPDS),
-                     mDS = mnmajor_base<128>(sPDS + tile_bytes(128)), kDS = kmajor_base<128>(sPDS + tile_bytes(128));
-      // merged views: second 32-column block found at a leading-dimension offset of the tile distance
-      const uint64_t dQQb = smem_desc(sStage, 2 * Cfg::D_BYTES, 8 * 64, 64);
-      const uint64_t dKKc = smem_desc(sK, Cfg::OFF_KC - Cfg::OFF_K, 8 * 64, 64);
-      const DescBase mQQb{(uint32_t)dQQb, (uint32_t)(dQQb >> 32)}, mKKc{(uint32_t)dKKc, (uint32_t)(dKKc >> 32)};
       constexpr uint32_t idTM = instr_desc(kBf16, true, true, 128, D + RPX);   // dK|dKb merged
       constexpr uint32_t idQM = instr_desc(kBf16, false, true, 128, D + RPX);  // dQ|dQb merged
-      auto issue_S_dP = [&](int it) {
-        const int st = it & 1;
-        const uint32_t so = st * Cfg::STAGE_BYTES;
-        mbar_wait(qdo_full + 8 * st, (it >> 1) & 1, abort_flag, a.status);
-        tc_fence_after_sync();
-        // bias products first, into the empty accumulator (large factor terms cancel among themselves)
-        if (RP) {
+      mbar_wait(kv_full, 0, abort_flag, a.status);
+      tc_fence_after_sync();
+      if (role == 0) {
+        // descriptor views built once (stage 0); each MMA adds a constant to the address field
+        const DescBase kQ = kmajor_base<D>(sStage), kDO = kmajor_base<D>(sStage + Cfg::D_BYTES),
+                       kQb = kmajor_base<RPX>(sStage + 2 * Cfg::D_BYTES), kK = kmajor_base<D>(sK),
+                       kKb = kmajor_base<RPX>(sKb), kV = kmajor_base<D>(sV);
+#pragma unroll 1
+        for (int it = 0; it < n_it; ++it) {
+          const int st = it & 1;
+          const uint32_t so = st * Cfg::STAGE_BYTES;
+          if (it > 0) {  // the compute warps hold S and dP of the previous tile in registers
+            mbar_wait(sdp_read, (it - 1) & 1, abort_flag, a.status);
+            tc_fence_after_sync();
+          }
+          mbar_wait(qdo_full + 8 * st, (it >> 1) & 1, abort_flag, a.status);
+          tc_fence_after_sync();
+          FB_TRACE_MARK(it, 4);
+          // bias products first, into the empty accumulator (large factor terms cancel among themselves)
+          if (RP) {
 #pragma unroll
-          for (int s = 0; s < RPX / 16; ++s)
-            umma_ss(tmem + Cfg::T_S, desc_at(kQb, so + kmajor_step<RPX>(s)), desc_at(kKb, kmajor_step<RPX>(s)), idS,
-                    s > 0);
-        }
+            for (int s = 0; s < RPX / 16; ++s)
+              umma_ss(tmem + Cfg::T_S, desc_at(kQb, so + kmajor_step<RPX>(s)), desc_at(kKb, kmajor_step<RPX>(s)), idS,
+                      s > 0);
+          }
 #pragma unroll
-        for (int t = 0; t < NQ; ++t) {  // query terms share the K tile
+          for (int t = 0; t < NQ; ++t) {  // query terms share the K tile
+#pragma unroll
+            for (int s = 0; s < D / 16; ++s)
+              umma_ss(tmem + Cfg::T_S, desc_at(kQ, so + (t ? Cfg::OFF_QLO : 0) + kmajor_step<D>(s)),
+                      desc_at(kK, kmajor_step<D>(s)), idS, (RP || t > 0 || s > 0) ? 1u : 0u);
+          }
+          umma_commit(s_full);
 #pragma unroll
           for (int s = 0; s < D / 16; ++s)
-            umma_ss(tmem + Cfg::T_S, desc_at(kQ, so + (t ? Cfg::OFF_QLO : 0) + kmajor_step<D>(s)),
-                    desc_at(kK, kmajor_step<D>(s)), idS, (RP || t > 0 || s > 0) ? 1u : 0u);
+            umma_ss(tmem + Cfg::T_DP, desc_at(kDO, so + kmajor_step<D>(s)), desc_at(kV, kmajor_step<D>(s)), idS,
+                    s > 0);
+          umma_commit(dp_full);
+          umma_commit(qdo_free + 8 * st);
+          FB_TRACE_MARK(it, 5);
         }
-        umma_commit(s_full);
-#pragma unroll
-        for (int s = 0; s < D / 16; ++s)
-          umma_ss(tmem + Cfg::T_DP, desc_at(kDO, so + kmajor_step<D>(s)), desc_at(kV, kmajor_step<D>(s)), idS, s > 0);
-        umma_commit(dp_full);
-      };
-      mbar_wait(kv_full, 0, abort_flag, a.status);
-      issue_S_dP(0);
-      for (int it = 0; it < n_it; ++it) {
-        const int st = it & 1;
-        const uint32_t so = st * Cfg::STAGE_BYTES;
-        const uint32_t po = (Cfg::PIPE ? st : 0) * Cfg::PDS_BYTES;
-        mbar_wait(pds_ready, it & 1, abort_flag, a.status);
-        tc_fence_after_sync();
-        // S and dP of the next query tile go first when P/dS are double-buffered: the compute warps then
-        // start on tile it+1 while the tensor core is still busy with dV/dK/dQ of tile it.
-        if (Cfg::PIPE && it + 1 < n_it) issue_S_dP(it + 1);
-        const uint32_t acc0 = it > 0 ? 1u : 0u;
-#pragma unroll
-        for (int s = 0; s < 8; ++s) {  // contraction over the 128 query rows
-          const uint32_t acc = (acc0 | (s > 0)) ? 1u : 0u;
-          umma_ss(tmem + Cfg::T_DV, desc_at(mP, po + mnmajor_step<128>(s)), desc_at(mDO, so + mnmajor_step<D>(s)),
-                  idTD, acc);
-          if (Cfg::MERGE) {
-            umma_ss(tmem + Cfg::T_DK, desc_at(mDS, po + mnmajor_step<128>(s)),
-                    desc_at(mQQb, so + mnmajor_step<D>(s)), idTM, acc);
-          } else {
-            umma_ss(tmem + Cfg::T_DK, desc_at(mDS, po + mnmajor_step<128>(s)), desc_at(mQ, so + mnmajor_step<D>(s)),
-                    idTD, acc);
-            if (RP)
-              umma_ss(tmem + Cfg::T_DKB, desc_at(mDS, po + mnmajor_step<128>(s)),
-                      desc_at(mQb, so + mnmajor_step<RPX>(s)), idTR, acc);
-          }
-          if (NQ == 2)  // dK += dS^T . lo(q*scale)
-            umma_ss(tmem + Cfg::T_DK, desc_at(mDS, po + mnmajor_step<128>(s)),
-                    desc_at(mQ, so + Cfg::OFF_QLO + mnmajor_step<D>(s)), idTD, 1);
-        }
-        if (it > 0) {
-          mbar_wait(dq_drained, (it - 1) & 1, abort_flag, a.status);
+      } else {
+        const DescBase mQ = mnmajor_base<D>(sStage), mDO = mnmajor_base<D>(sStage + Cfg::D_BYTES),
+                       mQb = mnmajor_base<RPX>(sStage + 2 * Cfg::D_BYTES), mK = mnmajor_base<D>(sK),
+                       mKc = mnmajor_base<RPX>(sKc), mP = mnmajor_base<128>(sPDS),
+                       mDS = mnmajor_base<128>(sPDS + tile_bytes(128)),
+                       kDS = kmajor_base<128>(sPDS + tile_bytes(128));
+        // merged views: second 32-column block found at a leading-dimension offset of the tile distance
+        const uint64_t dQQb = smem_desc(sStage, 2 * Cfg::D_BYTES, 8 * 64, 64);
+        const uint64_t dKKc = smem_desc(sK, Cfg::OFF_KC - Cfg::OFF_K, 8 * 64, 64);
+        const DescBase mQQb{(uint32_t)dQQb, (uint32_t)(dQQb >> 32)}, mKKc{(uint32_t)dKKc, (uint32_t)(dKKc >> 32)};
+#pragma unroll 1
+        for (int it = 0; it < n_it; ++it) {
+          const int st = it & 1;
+          const uint32_t so = st * Cfg::STAGE_BYTES;
+          const int buf = Cfg::PIPE ? st : 0;
+          const uint32_t po = buf * Cfg::PDS_BYTES;
+          const uint32_t acc0 = it > 0 ? 1u : 0u;
+          if (role != 3) mbar_wait(qdo_full + 8 * st, (it >> 1) & 1, abort_flag, a.status);
+          mbar_wait(pds_ready + 8 * (it & 1), (it >> 1) & 1, abort_flag, a.status);
           tc_fence_after_sync();
-        }
+          FB_TRACE_MARK(it, 4 + 2 * role);
+          if (FB_DBG(4)) {
+            if (role != 3) umma_commit(qdo_free + 8 * st);
+            if (role == 3) umma_commit(dq_full + 8 * (it % Cfg::NDQ));
+          } else if (role == 1) {
 #pragma unroll
-        for (int s = 0; s < 8; ++s) {  // contraction over the 128 keys
-          if (Cfg::MERGE) {
-            umma_ss(tmem + Cfg::T_DQ, desc_at(kDS, po + kmajor_step<128>(s)), desc_at(mKKc, mnmajor_step<D>(s)), idQM,
-                    s > 0);
+            for (int s = 0; s < 8; ++s)  // contraction over the 128 query rows
+              umma_ss(tmem + Cfg::T_DV, desc_at(mP, po + mnmajor_step<128>(s)), desc_at(mDO, so + mnmajor_step<D>(s)),
+                      idTD, (acc0 | (s > 0)) ? 1u : 0u);
+            if (RP && !Cfg::MERGE) {
+#pragma unroll
+              for (int s = 0; s < 8; ++s)
+                umma_ss(tmem + Cfg::T_DKB, desc_at(mDS, po + mnmajor_step<128>(s)),
+                        desc_at(mQb, so + mnmajor_step<RPX>(s)), idTR, (acc0 | (s > 0)) ? 1u : 0u);
+            }
+            umma_commit(qdo_free + 8 * st);
+          } else if (role == 2) {
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+              if (Cfg::MERGE)
+                umma_ss(tmem + Cfg::T_DK, desc_at(mDS, po + mnmajor_step<128>(s)),
+                        desc_at(mQQb, so + mnmajor_step<D>(s)), idTM, (acc0 | (s > 0)) ? 1u : 0u);
+              else
+                umma_ss(tmem + Cfg::T_DK, desc_at(mDS, po + mnmajor_step<128>(s)),
+                        desc_at(mQ, so + mnmajor_step<D>(s)), idTD, (acc0 | (s > 0)) ? 1u : 0u);
+            }
+            if (NQ == 2) {  // dK += dS^T . lo(q*scale)
+#pragma unroll
+              for (int s = 0; s < 8; ++s)
+                umma_ss(tmem + Cfg::T_DK, desc_at(mDS, po + mnmajor_step<128>(s)),
+                        desc_at(mQ, so + Cfg::OFF_QLO + mnmajor_step<D>(s)), idTD, 1);
+            }
+            umma_commit(qdo_free + 8 * st);
           } else {
-            umma_ss(tmem + Cfg::T_DQ, desc_at(kDS, po + kmajor_step<128>(s)), desc_at(mK, mnmajor_step<D>(s)), idQD,
-                    s > 0);
-            if (RP)
-              umma_ss(tmem + Cfg::T_DQB, desc_at(kDS, po + kmajor_step<128>(s)),
-                      desc_at(mKc, mnmajor_step<RPX>(s)), idQR, s > 0);
+            const int qb = it % Cfg::NDQ;  // dQ|dQb accumulator of this tile
+            const uint32_t tq = tmem + qb * Cfg::DQ_STRIDE;
+            if (it >= Cfg::NDQ) {  // the drain warpgroup has read the tile that used this accumulator last
+              mbar_wait(dq_drained + 8 * qb, (it / Cfg::NDQ - 1) & 1, abort_flag, a.status);
+              tc_fence_after_sync();
+            }
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {  // contraction over the 128 keys
+              if (Cfg::MERGE) {
+                umma_ss(tq + Cfg::T_DQ, desc_at(kDS, po + kmajor_step<128>(s)), desc_at(mKKc, mnmajor_step<D>(s)),
+                        idQM, s > 0);
+              } else {
+                umma_ss(tq + Cfg::T_DQ, desc_at(kDS, po + kmajor_step<128>(s)), desc_at(mK, mnmajor_step<D>(s)),
+                        idQD, s > 0);
+                if (RP)
+                  umma_ss(tq + Cfg::T_DQB, desc_at(kDS, po + kmajor_step<128>(s)),
+                          desc_at(mKc, mnmajor_step<RPX>(s)), idQR, s > 0);
+              }
+            }
+            umma_commit(dq_full + 8 * qb);
           }
+          umma_commit(pds_free + 8 * buf);  // this chain no longer reads the P/dS buffer of the tile
+          FB_TRACE_MARK(it, 5 + 2 * role);
         }
-        umma_commit(dq_full);
-        umma_commit(qdo_free + 8 * st);
-        umma_commit(pds_free + 8 * (Cfg::PIPE ? st : 0));  // P/dS buffer of this tile may be rewritten
-        if (!Cfg::PIPE && it + 1 < n_it) issue_S_dP(it + 1);
       }
-      umma_commit(all_done);  // every MMA of the CTA
+      umma_commit(all_done);  // every MMA of this thread
     }
   } else if (warp >= 8 && warp < 12) {
     // ------------------------------------------------------------------ drain warpgroup
@@ -291,15 +368,27 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll 1
       for (int it = 0; it < n_it; ++it) {
         const int grow = (i_begin + it) * 128 + row;
-        mbar_wait(dq_full, it & 1, abort_flag, a.status);
+        const int qb = it % Cfg::NDQ;
+        const uint32_t tq = tmem + qb * Cfg::DQ_STRIDE + lane_off;
+        mbar_wait(dq_full + 8 * qb, (it / Cfg::NDQ) & 1, abort_flag, a.status);
         tc_fence_after_sync();
+        if (warp == 8 && lane == 0) FB_TRACE_MARK(it, 12);
+        if (FB_DBG(2)) {
+          if (Cfg::PIPE) {
+            mbar_wait(pds_free + 8 * (it & 1), (it >> 1) & 1, abort_flag, a.status);
+            mbar_arrive_warp(stg_free + 8 * (it & 1));
+          }
+          tc_fence_before_sync();
+          mbar_arrive_warp(dq_drained + 8 * qb);
+          continue;
+        }
         if (!Cfg::PIPE) {
           // single P/dS buffer: no spare tile to stage in, reduce straight from registers (one row per thread)
           float* dst = a.dq_acc + (((int64_t)b * a.Sq + grow) * a.H + h) * D;
 #pragma unroll 1
           for (int c0 = 0; c0 < D; c0 += 32) {
             uint32_t r[32];
-            tmem_ld32(tmem + Cfg::T_DQ + lane_off + c0, r);
+            tmem_ld32(tq + Cfg::T_DQ + c0, r);
             tmem_wait_ld(r);
             if (grow < a.Sq) {
 #pragma unroll
@@ -309,39 +398,34 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
           }
         } else {
-          // dQ tile: TMEM -> registers -> shared-memory staging ([128 rows][D floats], 16-byte chunks XOR-swizzled
-          // by row) -> vector reductions with 8 consecutive lanes covering one 128-byte line of a row.  Row-per-
-          // thread reductions would put 32 different lines into every instruction and crowd the load/store unit
-          // that the compute warps need for their P/dS stores.  The staging area is the P tile of the buffer the
-          // MMAs of this query tile have finished reading; it is handed back through stg_free.
+          // dQ tile: TMEM -> registers -> shared-memory staging -> ONE bulk reduction into the fp32 accumulator.
+          // Per-thread vector reductions (32 per row) crowd the load/store unit that the compute warps need for
+          // their P/dS stores and row statistics; the bulk form is executed by the copy engine.  The staging area
+          // is the P tile of the buffer the MMAs of this query tile have finished reading; it is handed back
+          // through stg_free.
           const int buf = Cfg::PIPE ? (it & 1) : 0;
-          uint8_t* stage = smem + Cfg::OFF_PDS + buf * Cfg::PDS_BYTES;
-          constexpr int CPR = D / 4;  // 16-byte chunks per row
-          auto stage_off = [&](int r, int ch) {
-            return (ch >> 3) * (128 * 128) + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
-          };
+          const uint32_t stage = sPDS + buf * Cfg::PDS_BYTES;
+          // dq_full only covers the dQ chain: the dV chain (another thread) must be done with the P tile as well
+          mbar_wait(pds_free + 8 * buf, (it >> 1) & 1, abort_flag, a.status);
 #pragma unroll 1
           for (int c0 = 0; c0 < D; c0 += 16) {
             uint32_t r[16];
-            tmem_ld16(tmem + Cfg::T_DQ + lane_off + c0, r);
+            tmem_ld16(tq + Cfg::T_DQ + c0, r);
             tmem_wait_ld(r);
 #pragma unroll
             for (int g = 0; g < 4; ++g)
-              *reinterpret_cast<uint4*>(stage + stage_off(row, c0 / 4 + g)) =
-                  make_uint4(r[g * 4], r[g * 4 + 1], r[g * 4 + 2], r[g * 4 + 3]);
+              st_shared_v4(stage + dq_stage_off(row, c0 / 4 + g), r[g * 4], r[g * 4 + 1], r[g * 4 + 2], r[g * 4 + 3]);
           }
+          fence_proxy_async_smem();  // the staged tile becomes visible to the copy engine
           asm volatile("bar.sync 3, 128;" ::: "memory");  // the drain warpgroup only
-          const int q0d = (i_begin + it) * 128;
-          const int tid = (warp & 3) * 32 + lane;  // 0..127
-#pragma unroll 1
-          for (int i = 0; i < (128 * CPR) / 128; ++i) {
-            const int cid = i * 128 + tid;
-            const int rr = cid / CPR, ch = cid % CPR;
-            const float4 v = *reinterpret_cast<const float4*>(stage + stage_off(rr, ch));
-            if (q0d + rr < a.Sq)
-              red_add_v4(a.dq_acc + (((int64_t)b * a.Sq + q0d + rr) * a.H + h) * D + ch * 4, v.x, v.y, v.z, v.w);
+          if (warp == 8 && lane == 0) {
+            if (!FB_DBG(1))
+              bulk_reduce_add_f32(a.dq_acc + ((int64_t)bh * a.nq_tiles + (i_begin + it)) * (128 * D), stage,
+                                  128 * D * 4);
+            bulk_commit_group();
+            bulk_wait_group_read0();
+            mbar_arrive(stg_free + 8 * buf);  // staging reads done: the P tile may be rewritten
           }
-          mbar_arrive_warp(stg_free + 8 * buf);  // staging reads done: the P tile may be rewritten
         }
         if (RP) {
           // dq_bias = dS . k_bias, evaluated per group of 32 keys as dS16 . (k_bias - c) + c * rowsum_fp32(dS)
@@ -357,9 +441,9 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll 1
           for (int c0 = 0; c0 < RPX && c0 < used; c0 += 16) {
             uint32_t r[16];
-            tmem_ld16(tmem + Cfg::T_DQB + lane_off + c0, r);
+            tmem_ld16(tq + Cfg::T_DQB + c0, r);
             tmem_wait_ld(r);
-            if (grow < a.Sq) {
+            if (grow < a.Sq && !FB_DBG(1)) {
 #pragma unroll
               for (int i = 0; i < 16; ++i) {
                 const int c = c0 + i;
@@ -376,8 +460,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
         }
         tc_fence_before_sync();
-        mbar_arrive(dq_drained);
+        if (warp == 8 && lane == 0) FB_TRACE_MARK(it, 13);
+        mbar_arrive_warp(dq_drained + 8 * qb);
       }
+      if (Cfg::PIPE && warp == 8 && lane == 0) bulk_wait_group0();  // reductions complete before the CTA exits
     }
   } else if (n_it > 0) {
     // ------------------------------------------------------------------ compute warpgroups (warps 0-7)
@@ -403,9 +489,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int g = (i_begin + it) * 128 + row;
       lse_raw = INFINITY;
       dlt = 0.f;
-      if (it < n_it && g < a.Sq) {
-        lse_raw = __ldg(a.lse + (int64_t)bh * a.lse_stride_bh + g);
-        dlt = __ldg(a.delta + (int64_t)bh * a.lse_stride_bh + g);
+      if (it < n_it && g < a.Sq && !FB_DBG(64)) {
+        // volatile: the compiler must not sink the loads to their use one tile later
+        asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(lse_raw) : "l"(a.lse + (int64_t)bh * a.lse_stride_bh + g));
+        asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(dlt) : "l"(a.delta + (int64_t)bh * a.lse_stride_bh + g));
       }
     };
 
@@ -417,11 +504,13 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int grow = q0 + row;
       // a row that saw no key has lse = -inf: make its probabilities exactly zero
       const float lse2_cur = lse_raw == -INFINITY ? INFINITY : lse_raw * kLog2e, dlt_cur = dlt;
+      if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 17);
       load_row_stats(it + 1, lse_raw, dlt);  // next tile's statistics: the loads complete under this tile's math
-      uint8_t* sP_gen = smem + Cfg::OFF_PDS + (Cfg::PIPE ? (it & 1) : 0) * Cfg::PDS_BYTES;
-      uint8_t* sDS_gen = sP_gen + tile_bytes(128);
+      if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 18);
+      const uint32_t sP_cur = sPDS + (Cfg::PIPE ? (it & 1) : 0) * Cfg::PDS_BYTES;  // P tile, dS tile behind it
       const bool need_mask = (a.causal && k0 + 127 > q0) || (k0 + 128 > a.Sk);
       float ds_sum0 = 0.f, ds_sum1 = 0.f;  // fp32 row sums of dS over this thread's two 32-column groups
+      if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 14);
       mbar_wait(s_full, it & 1, abort_flag, a.status);
       mbar_wait(dp_full, it & 1, abort_flag, a.status);
       // the MMAs that read this P/dS buffer last (query tile it - NBUF) have completed
@@ -434,22 +523,28 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
       tc_fence_after_sync();
+      if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 0);
       uint32_t rs0[32], rd0[32];
       auto chunk = [&](uint32_t (&rs)[32], uint32_t (&rd)[32], int c) {
         const int col0 = wg * 64 + c * 32;
         float sum0 = 0.f, sum1 = 0.f;
+        // the masked and the unmasked tile get separate straight-line loops: a per-element test of need_mask
+        // becomes a branch per element and the 32 elements then run one after the other
+        auto elems = [&](auto masked) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float p = fast_exp2(fmaf(__uint_as_float(rs[i]), sl2, -lse2_cur));
-          if (need_mask) {
-            const int col = k0 + col0 + i;
-            if (col >= a.Sk || (a.causal && col > grow)) p = 0.f;
+          for (int i = 0; i < 32; ++i) {
+            float p = fast_exp2(fmaf(__uint_as_float(rs[i]), sl2, -lse2_cur));
+            if (decltype(masked)::value) {
+              const int col = k0 + col0 + i;
+              if (col >= a.Sk || (a.causal && col > grow)) p = 0.f;
+            }
+            const float ds = p * (__uint_as_float(rd[i]) - dlt_cur);
+            if (i & 1) sum1 += ds; else sum0 += ds;
+            rs[i] = __float_as_uint(p);
+            rd[i] = __float_as_uint(ds);
           }
-          const float ds = p * (__uint_as_float(rd[i]) - dlt_cur);
-          if (i & 1) sum1 += ds; else sum0 += ds;
-          rs[i] = __float_as_uint(p);
-          rd[i] = __float_as_uint(ds);
-        }
+        };
+        if (need_mask) elems(std::true_type{}); else elems(std::false_type{});
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           uint4 wp, wd;
@@ -462,8 +557,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           wd.z = Pack2<T>::pack(__uint_as_float(rd[g * 8 + 4]), __uint_as_float(rd[g * 8 + 5]));
           wd.w = Pack2<T>::pack(__uint_as_float(rd[g * 8 + 6]), __uint_as_float(rd[g * 8 + 7]));
           const uint32_t off = tile_chunk_offset<128>(row, col0 + g * 8);
-          *reinterpret_cast<uint4*>(sP_gen + off) = wp;
-          *reinterpret_cast<uint4*>(sDS_gen + off) = wd;
+          st_shared_v4(sP_cur + off, wp.x, wp.y, wp.z, wp.w);
+          st_shared_v4(sP_cur + tile_bytes(128) + off, wd.x, wd.y, wd.z, wd.w);
         }
         return sum0 + sum1;
       };
@@ -474,7 +569,20 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_ld32(tDl + c * 32, rd0);
         tmem_wait_ld(rs0);
         tmem_wait_ld(rd0);
+        if (c == 1) {  // S and dP are in registers: the tensor core may overwrite them with the next tile's
+          tc_fence_before_sync();
+          mbar_arrive_warp(sdp_read);
+        }
+        if (FB_DBG(32)) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            rs0[i] = 0u;
+            rd0[i] = 0u;
+          }
+        }
+        if (lane == 0 && warp == 0) FB_TRACE_MARK(it, c == 0 ? 2 : 15);
         const float sum = chunk(rs0, rd0, c);
+        if (lane == 0 && warp == 0 && c == 0) FB_TRACE_MARK(it, 3);
         if (c == 0) ds_sum0 = sum; else ds_sum1 = sum;
       }
       if (RP) {
@@ -483,9 +591,12 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         s_rowsum[(2 * wg) * 128 + row] = ds_sum0;
         s_rowsum[(2 * wg + 1) * 128 + row] = ds_sum1;
       }
+      if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 19);
       fence_proxy_async_smem();
       tc_fence_before_sync();
-      mbar_arrive(pds_ready);
+      if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 1);
+      mbar_arrive_warp(pds_ready + 8 * (it & 1));
+      if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 16);
     }
     // the dV and dK|dKb accumulators are final once every MMA of the CTA has completed
     mbar_wait(all_done, 0, abort_flag, a.status);
@@ -561,10 +672,12 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 }
 
-// dq = T(scale * acc), acc laid out (B, Sq, H, D) fp32
+// dq = T(scale * acc).  acc is fp32, laid out (B, Sq, H, D), or -- `tiled` -- per (batch, head, query tile) as the
+// staged [128][D] tile of dq_stage_off.
 template <typename T>
 __global__ void __launch_bounds__(256) dq_store_kernel(const float* __restrict__ acc, T* __restrict__ dq, int B, int Sq,
-                                                       int H, int D, int64_t sb, int64_t sh, int64_t ss, float scale) {
+                                                       int H, int D, int64_t sb, int64_t sh, int64_t ss, float scale,
+                                                       int tiled) {
   const int64_t idx = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;  // 8 consecutive d
   const int64_t total = (int64_t)B * Sq * H * D;
   if (idx >= total) return;
@@ -572,8 +685,16 @@ __global__ void __launch_bounds__(256) dq_store_kernel(const float* __restrict__
   const int h = (int)((idx / D) % H);
   const int s = (int)((idx / ((int64_t)D * H)) % Sq);
   const int b = (int)(idx / ((int64_t)D * H * Sq));
-  const float4 x = *reinterpret_cast<const float4*>(acc + idx);
-  const float4 y = *reinterpret_cast<const float4*>(acc + idx + 4);
+  float4 x, y;
+  if (tiled) {
+    const int nq_tiles = (Sq + 127) / 128;
+    const char* tile = reinterpret_cast<const char*>(acc + (((int64_t)b * H + h) * nq_tiles + s / 128) * (128 * D));
+    x = *reinterpret_cast<const float4*>(tile + dq_stage_off(s % 128, d / 4));
+    y = *reinterpret_cast<const float4*>(tile + dq_stage_off(s % 128, d / 4 + 1));
+  } else {
+    x = *reinterpret_cast<const float4*>(acc + idx);
+    y = *reinterpret_cast<const float4*>(acc + idx + 4);
+  }
   uint4 w;
   w.x = Pack2<T>::pack(x.x * scale, x.y * scale);
   w.y = Pack2<T>::pack(x.z * scale, x.w * scale);
@@ -585,6 +706,13 @@ __global__ void __launch_bounds__(256) dq_store_kernel(const float* __restrict__
 // ------------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------------
+#ifdef FB_TRACE
+}  // namespace fb
+extern "C" int fb_debug_trace_bwd(long long* out, int n) {
+  return (int)cudaMemcpyFromSymbol(out, fb::g_bwd_trace, sizeof(long long) * (n < 2048 ? n : 2048));
+}
+namespace fb {
+#endif
 int store_factor_grads_from(const fb_params* p, float* dqb, float* dkb, cudaStream_t st);  // fb_general.cu
 
 static bool rows_16b_ok(const void* ptr, const int64_t* st) {
@@ -604,7 +732,8 @@ static BwdWs bwd_layout(const fb_params* p, const PackPlan& plan) {
   w.off_kcenter = w.off_kpack + plan.k_bytes;
   w.off_qs = w.off_kcenter + plan.k_bytes;
   w.off_dq = w.off_qs + plan.qs_bytes;
-  const size_t dq = round256((size_t)p->B * p->Sq * p->H * p->D * 4);
+  // query rows padded to whole tiles: the bulk reductions of the backward write whole [128][D] tiles
+  const size_t dq = round256((size_t)p->B * ((p->Sq + 127) / 128) * 128 * p->H * p->D * 4);
   const size_t dqb = p->R ? round256((size_t)plan.Bq * p->Sq * plan.Hq * p->R * 4) : 0;
   const size_t dkb = p->R ? round256((size_t)plan.Bk * p->Sk * plan.Hk * p->R * 4) : 0;
   w.off_dqb = w.off_dq + dq;
@@ -713,6 +842,10 @@ static int launch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t s
   a.k_bias = p->k_bias;
   for (int i = 0; i < 3; ++i) a.kb_stride[i] = p->k_bias_stride[i];
   a.status = p->status;
+  a.dbg = 0;
+#ifdef FB_TRACE
+  if (const char* e_dbg = getenv("FB_DBG")) a.dbg = atoi(e_dbg);
+#endif
   auto kern = bwd_sm100_kernel<T, D, RP, NQ>;
   static bool attr_done[64] = {};
   int dev = 0;
@@ -724,14 +857,14 @@ static int launch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t s
   }
   const unsigned grid = (unsigned)((int64_t)a.nk_tiles * p->B * p->H);
   prof_before(KC_BWD_MAIN, st);
-  kern<<<grid, 448, Cfg::SMEM, st>>>(tQ, tK, tV, tDO, tQb, tKb, tKc, a);
+  kern<<<grid, 544, Cfg::SMEM, st>>>(tQ, tK, tV, tDO, tQb, tKb, tKc, a);
   prof_after(KC_BWD_MAIN, st);
   note_launch();
   if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
   const int64_t n8 = ((int64_t)p->B * p->Sq * p->H * D) / 8;
   dq_store_kernel<T><<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(
       a.dq_acc, reinterpret_cast<T*>(p->dq), p->B, p->Sq, p->H, D, p->dq_stride[0], p->dq_stride[1], p->dq_stride[2],
-      p->softmax_scale);
+      p->softmax_scale, Cfg::PIPE ? 1 : 0);
   note_launch();
   if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
   if (p->R > 0) return store_factor_grads_from(p, a.dqb_acc, a.dkb_acc, st);

@@ -295,6 +295,11 @@ __device__ __forceinline__ void tmem_wait_ld(uint32_t (&r)[16]) {
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// 16-byte store to a shared-memory address (32-bit shared-window address, no generic-address translation)
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------
 // Small math / conversion helpers
 // ---------------------------------------------------------------------------------------------
