@@ -65,7 +65,7 @@ __device__ __forceinline__ void tma_tile_4d(uint32_t dst, const CUtensorMap* m, 
 }
 
 template <typename T, int D, int RP, int NQ>
-__global__ void __launch_bounds__(192, FwdCfg<D, RP, NQ>::MINB)
+__global__ void __launch_bounds__(224, FwdCfg<D, RP, NQ>::MINB)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmQb,
                  const __grid_constant__ CUtensorMap tmKb, const FwdArgs a) {
@@ -82,7 +82,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
   // barrier slots
   const uint32_t bar0 = smem_u32(bars);
-  const uint32_t q_full = bar0, s_full = bar0 + 8, p_ready = bar0 + 16, pv_done = bar0 + 24;
+  const uint32_t q_full = bar0, s_full = bar0 + 8, p_ready = bar0 + 16, pv_done = bar0 + 24, s_read = bar0 + 176;
   const uint32_t k_full = bar0 + 32, k_free = bar0 + 64, v_full = bar0 + 96, v_free = bar0 + 128;  // 4 slots each
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::OFF_BAR + 160);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::OFF_BAR + 168);
@@ -108,6 +108,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(q_full, 1);
       mbar_init(s_full, 1);
       mbar_init(p_ready, 4);  // one arrival per softmax warp
+      mbar_init(s_read, 4);   // likewise: the logits of the tile are in registers
       mbar_init(pv_done, 1);
       for (int i = 0; i < 4; ++i) {
         mbar_init(k_full + 8 * i, 1);
@@ -151,13 +152,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     }
   } else if (warp == 5) {
-    // ------------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------------------------ MMA issuer: S = [Q|Qb].[K|Kb]^T
     if (lane == 0) {
       constexpr uint32_t idS = instr_desc(kBf16, false, false, 128, 128);
-      constexpr uint32_t idO = instr_desc(kBf16, false, true, 128, D);
       // descriptor views built once; each MMA only adds a constant to the start-address field
       const DescBase dQ = kmajor_base<D>(sQ), dQb = kmajor_base<RPX>(sQb), dK = kmajor_base<D>(sK),
-                     dKb = kmajor_base<RPX>(sKb), dV = mnmajor_base<D>(sV);
+                     dKb = kmajor_base<RPX>(sKb);
       auto issue_S = [&](int j) {
         const int ks = j % KST;
         mbar_wait(k_full + 8 * ks, (j / KST) & 1, abort_flag, a.status);
@@ -182,13 +182,25 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         umma_commit(k_free + 8 * ks);
       };
       mbar_wait(q_full, 0, abort_flag, a.status);
-      issue_S(0);
       for (int j = 0; j < n_kv; ++j) {
-        mbar_wait(p_ready, j & 1, abort_flag, a.status);
-        tc_fence_after_sync();
-        if (j + 1 < n_kv) issue_S(j + 1);
+        if (j > 0) {  // the softmax warps hold the logits of the previous key tile in registers
+          mbar_wait(s_read, (j - 1) & 1, abort_flag, a.status);
+          tc_fence_after_sync();
+        }
+        issue_S(j);
+      }
+    }
+  } else if (warp == 6) {
+    // ------------------------------------------------------------------ MMA issuer: O += P.V
+    // A second issuing thread on another warp scheduler: S of the next key tile and P.V of this one are
+    // issued concurrently (an issuing thread only gets a slot when the softmax warps of its scheduler stall).
+    if (lane == 0) {
+      constexpr uint32_t idO = instr_desc(kBf16, false, true, 128, D);
+      const DescBase dV = mnmajor_base<D>(sV);
+      for (int j = 0; j < n_kv; ++j) {
         const int vs = j % VST;
         mbar_wait(v_full + 8 * vs, (j / VST) & 1, abort_flag, a.status);
+        mbar_wait(p_ready, j & 1, abort_flag, a.status);
         tc_fence_after_sync();
         const uint32_t vo = vs * Cfg::Q_BYTES;
 #pragma unroll
@@ -299,6 +311,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tmem_ld32(tSl + 96, rb);
       chunk_exp(ra, 2);
       tmem_wait_ld(rb);
+      tc_fence_before_sync();
+      mbar_arrive_warp(s_read);  // S is in registers: the tensor core may start on the next key tile
       chunk_exp(rb, 3);
       l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       tmem_wait_st();
@@ -424,7 +438,7 @@ static int launch_fwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t s
   }
   const unsigned grid = (unsigned)((int64_t)a.nq_tiles * p->B * p->H);
   prof_before(KC_FWD_MAIN, st);
-  kern<<<grid, 192, Cfg::SMEM, st>>>(tQ, tK, tV, tQb, tKb, a);
+  kern<<<grid, 224, Cfg::SMEM, st>>>(tQ, tK, tV, tQb, tKb, a);
   prof_after(KC_FWD_MAIN, st);
   note_launch();
   return (int)cudaGetLastError();
