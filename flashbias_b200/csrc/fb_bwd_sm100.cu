@@ -53,36 +53,51 @@ struct BwdCfg {
   static constexpr int RPX = RP ? RP : 16;
   static constexpr int D_BYTES = tile_bytes(D);
   static constexpr int R_BYTES = RP ? tile_bytes(RPX) : 0;
-  // one stage: Q (or hi of q*scale), dO, Qb, then lo of q*scale when the query operand is split
-  static constexpr int STAGE_BYTES = (1 + NQ) * D_BYTES + R_BYTES;
-  static constexpr int OFF_QLO = 2 * D_BYTES + R_BYTES;
-  static constexpr int PDS_BYTES = 2 * tile_bytes(128);      // P then dS
-  // P and dS tiles are double-buffered when shared memory allows it, so that the exponentials of
-  // query tile i+1 overlap the dV/dK/dQ MMAs of query tile i.
-  static constexpr bool PIPE =
-      (D == 32) && (2 * D_BYTES + 2 * R_BYTES + 2 * STAGE_BYTES + 2 * PDS_BYTES + 12288 <= 227 * 1024);
-  static constexpr int NBUF = PIPE ? 2 : 1;
-  // [Q|Qb] and [K|Kc] read as one MN-major operand of N = D + RP (two 64-byte-swizzled tiles)
-  static constexpr bool MERGE = (D == 32 && RP == 32);
+  // centred k-side factor tile: as wide as a head_dim-32 tile, so that [K | Kc] reads as one MMA operand
+  static constexpr int RC = RP ? ((D == 32 && RP < 32) ? 32 : RP) : 0;
+  static constexpr int RCX = RC ? RC : 16;
+  static constexpr int RC_BYTES = RC ? tile_bytes(RCX) : 0;
+  // one stage: the query terms (q, or hi then lo of q*scale), Qb, dO
+  static constexpr int OFF_QLO = D_BYTES;
+  static constexpr int OFF_QB = NQ * D_BYTES;
+  static constexpr int OFF_DO = OFF_QB + R_BYTES;
+  static constexpr int STAGE_BYTES = OFF_DO + D_BYTES;
+  static constexpr int PDS_BYTES = 2 * tile_bytes(128);  // P then dS
+  // Operands that share the A tile are read as ONE MN-major B operand of several 32-column blocks (head_dim 32:
+  // 64-byte-swizzled tiles at a constant distance), which saves the repeated shared-memory fetch of A:
+  //   dK chain:  dS^T . [q hi | q lo | Qb]   (Qb only when it is 32 columns wide)
+  //   dQ chain:  dS   . [K | Kc]
+  static constexpr int KBLK = (D == 32) ? NQ + (RP == 32 ? 1 : 0) : 1;
+  static constexpr bool MERGE_K = KBLK > 1;
+  static constexpr bool DKB_MERGED = (D == 32 && RP == 32);  // dKb columns sit behind the dK columns
+  static constexpr bool MERGE_Q = (D == 32 && RC == 32);
   static constexpr int OFF_K = 0;
   static constexpr int OFF_KB = OFF_K + D_BYTES;
-  static constexpr int OFF_KC = OFF_KB + R_BYTES;  // centered k_bias tile (dq_bias only)
-  static constexpr int OFF_V = OFF_KC + R_BYTES;
+  static constexpr int OFF_KC = OFF_KB + R_BYTES;  // centred k_bias tile (dq_bias only)
+  static constexpr int OFF_V = OFF_KC + RC_BYTES;
   static constexpr int OFF_STAGE = OFF_V + D_BYTES;
   static constexpr int OFF_PDS = OFF_STAGE + 2 * STAGE_BYTES;
+  static constexpr int TAIL_BYTES = 256 + 8192 + 4 * RCX * 4 + 1024;  // barriers, row sums, centre keys, alignment
+  // P and dS tiles are double-buffered when shared memory allows it, so that the exponentials of
+  // query tile i+1 overlap the dV/dK/dQ MMAs of query tile i.
+  static constexpr bool PIPE = (D == 32) && (OFF_PDS + 2 * PDS_BYTES + TAIL_BYTES <= 227 * 1024);
+  static constexpr int NBUF = PIPE ? 2 : 1;
   static constexpr int OFF_BAR = OFF_PDS + NBUF * PDS_BYTES;
-  static constexpr int OFF_ROWSUM = OFF_BAR + 256;       // 4 x 4 x 128 floats: dS row sums per 32-key group
-  static constexpr int OFF_KBC = OFF_ROWSUM + 8192;      // 4 x RPX floats: k_bias of the 4 centre keys
-  static constexpr int SMEM = OFF_KBC + 4 * RPX * 4 + 1024;
+  static constexpr int OFF_ROWSUM = OFF_BAR + 256;   // 4 x 4 x 128 floats: dS row sums per 32-key group
+  static constexpr int OFF_KBC = OFF_ROWSUM + 8192;  // 4 x RCX floats: k_bias of the 4 centre keys
+  static constexpr int SMEM = OFF_PDS + NBUF * PDS_BYTES + TAIL_BYTES;
   // tensor-memory columns
-  static constexpr int T_S = 0, T_DP = 128, T_DV = 256, T_DK = T_DV + D, T_DKB = T_DK + D, T_DQ = T_DKB + RP,
-                       T_DQB = T_DQ + D, T_END = T_DQB + RP;
-  static_assert(T_END <= 512, "tensor memory budget exceeded");
+  static constexpr int DK_COLS = MERGE_K ? 32 * KBLK : D;  // a split query adds its lo product in place otherwise
+  static constexpr int T_S = 0, T_DP = 128, T_DV = 256, T_DK = T_DV + D;
+  static constexpr int T_DKB = DKB_MERGED ? T_DK + 32 * NQ : T_DK + DK_COLS;
+  static constexpr int T_DQ = T_DK + DK_COLS + (DKB_MERGED ? 0 : RP);
+  static constexpr int T_DQB = T_DQ + D, T_END = T_DQB + RC;
   // a second dQ|dQb accumulator when tensor memory has room: the dQ MMAs of query tile i+1 then do not wait
   // for the drain of tile i
-  static constexpr int NDQ = (T_END + D + RP <= 512) ? 2 : 1;
+  static constexpr int NDQ = (T_END + D + RC <= 512) ? 2 : 1;
   static constexpr int DQ_STRIDE = T_END - T_DQ;  // columns between the two accumulators
-  static constexpr bool FITS = SMEM <= 227 * 1024;  // otherwise the variant is not built (shape-generic kernels)
+  // otherwise the variant is not built (shape-generic kernels take the problem)
+  static constexpr bool FITS = SMEM <= 227 * 1024 && T_END <= 512;
 };
 
 template <int C>
@@ -201,10 +216,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (lane == 0 && n_it > 0) {
       const int hq = a.hq_bcast ? 0 : h, bq = a.bq_bcast ? 0 : b;
       const int hk = a.hk_bcast ? 0 : h, bk = a.bk_bcast ? 0 : b;
-      mbar_expect_tx(kv_full, 2 * Cfg::D_BYTES + 2 * Cfg::R_BYTES);
+      mbar_expect_tx(kv_full, 2 * Cfg::D_BYTES + Cfg::R_BYTES + Cfg::RC_BYTES);
       tma_tile_bwd<D>(sK, &tmK, kv_full, k0, h, b);
       if (RP) tma_tile_bwd<RPX>(sKb, &tmKb, kv_full, k0, hk, bk);
-      if (RP) tma_tile_bwd<RPX>(sKc, &tmKc, kv_full, k0, hk, bk);
+      if (RP) tma_tile_bwd<Cfg::RCX>(sKc, &tmKc, kv_full, k0, hk, bk);
       tma_tile_bwd<D>(sV, &tmV, kv_full, k0, h, b);
       for (int it = 0; it < n_it; ++it) {
         const int st = it & 1;
@@ -213,9 +228,9 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         mbar_expect_tx(qdo_full + 8 * st, Cfg::STAGE_BYTES);
         const int q0 = (i_begin + it) * 128;
         tma_tile_bwd<D>(base, &tmQ, qdo_full + 8 * st, q0, h, b);
-        tma_tile_bwd<D>(base + Cfg::D_BYTES, &tmDO, qdo_full + 8 * st, q0, h, b);
-        if (RP) tma_tile_bwd<RPX>(base + 2 * Cfg::D_BYTES, &tmQb, qdo_full + 8 * st, q0, hq, bq);
         if (NQ == 2) tma_tile_bwd<D>(base + Cfg::OFF_QLO, &tmQ, qdo_full + 8 * st, q0, h, b, D);
+        if (RP) tma_tile_bwd<RPX>(base + Cfg::OFF_QB, &tmQb, qdo_full + 8 * st, q0, hq, bq);
+        tma_tile_bwd<D>(base + Cfg::OFF_DO, &tmDO, qdo_full + 8 * st, q0, h, b);
       }
     }
   } else if (warp >= 13) {
@@ -232,15 +247,12 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       constexpr uint32_t idTD = instr_desc(kBf16, true, true, 128, D);     // dV, dK: A^T (MN-major), B MN-major
       constexpr uint32_t idTR = instr_desc(kBf16, true, true, 128, RPX);   // dKb
       constexpr uint32_t idQD = instr_desc(kBf16, false, true, 128, D);    // dQ: A K-major, B MN-major
-      constexpr uint32_t idQR = instr_desc(kBf16, false, true, 128, RPX);  // dQb
-      constexpr uint32_t idTM = instr_desc(kBf16, true, true, 128, D + RPX);   // dK|dKb merged
-      constexpr uint32_t idQM = instr_desc(kBf16, false, true, 128, D + RPX);  // dQ|dQb merged
       mbar_wait(kv_full, 0, abort_flag, a.status);
       tc_fence_after_sync();
       if (role == 0) {
         // descriptor views built once (stage 0); each MMA adds a constant to the address field
-        const DescBase kQ = kmajor_base<D>(sStage), kDO = kmajor_base<D>(sStage + Cfg::D_BYTES),
-                       kQb = kmajor_base<RPX>(sStage + 2 * Cfg::D_BYTES), kK = kmajor_base<D>(sK),
+        const DescBase kQ = kmajor_base<D>(sStage), kDO = kmajor_base<D>(sStage + Cfg::OFF_DO),
+                       kQb = kmajor_base<RPX>(sStage + Cfg::OFF_QB), kK = kmajor_base<D>(sK),
                        kKb = kmajor_base<RPX>(sKb), kV = kmajor_base<D>(sV);
 #pragma unroll 1
         for (int it = 0; it < n_it; ++it) {
@@ -277,15 +289,19 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           FB_TRACE_MARK(it, 5);
         }
       } else {
-        const DescBase mQ = mnmajor_base<D>(sStage), mDO = mnmajor_base<D>(sStage + Cfg::D_BYTES),
-                       mQb = mnmajor_base<RPX>(sStage + 2 * Cfg::D_BYTES), mK = mnmajor_base<D>(sK),
-                       mKc = mnmajor_base<RPX>(sKc), mP = mnmajor_base<128>(sPDS),
+        const DescBase mQ = mnmajor_base<D>(sStage), mDO = mnmajor_base<D>(sStage + Cfg::OFF_DO),
+                       mQb = mnmajor_base<RPX>(sStage + Cfg::OFF_QB), mK = mnmajor_base<D>(sK),
+                       mKc = mnmajor_base<Cfg::RCX>(sKc), mP = mnmajor_base<128>(sPDS),
                        mDS = mnmajor_base<128>(sPDS + tile_bytes(128)),
                        kDS = kmajor_base<128>(sPDS + tile_bytes(128));
-        // merged views: second 32-column block found at a leading-dimension offset of the tile distance
-        const uint64_t dQQb = smem_desc(sStage, 2 * Cfg::D_BYTES, 8 * 64, 64);
+        // merged views (head_dim 32): 32-column blocks of 64-byte-swizzled rows, the next block found at a
+        // leading-dimension offset of the distance between the tiles
+        const uint64_t dQall = smem_desc(sStage, Cfg::D_BYTES, 8 * 64, 64);
         const uint64_t dKKc = smem_desc(sK, Cfg::OFF_KC - Cfg::OFF_K, 8 * 64, 64);
-        const DescBase mQQb{(uint32_t)dQQb, (uint32_t)(dQQb >> 32)}, mKKc{(uint32_t)dKKc, (uint32_t)(dKKc >> 32)};
+        const DescBase mQall{(uint32_t)dQall, (uint32_t)(dQall >> 32)}, mKKc{(uint32_t)dKKc, (uint32_t)(dKKc >> 32)};
+        constexpr uint32_t idKM = instr_desc(kBf16, true, true, 128, Cfg::MERGE_K ? 32 * Cfg::KBLK : 32);  // merged dK
+        constexpr uint32_t idQM = instr_desc(kBf16, false, true, 128, D + Cfg::RCX);                       // dQ|dQb
+        constexpr uint32_t idQC = instr_desc(kBf16, false, true, 128, Cfg::RCX);                           // dQb alone
 #pragma unroll 1
         for (int it = 0; it < n_it; ++it) {
           const int st = it & 1;
@@ -305,7 +321,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             for (int s = 0; s < 8; ++s)  // contraction over the 128 query rows
               umma_ss(tmem + Cfg::T_DV, desc_at(mP, po + mnmajor_step<128>(s)), desc_at(mDO, so + mnmajor_step<D>(s)),
                       idTD, (acc0 | (s > 0)) ? 1u : 0u);
-            if (RP && !Cfg::MERGE) {
+            if (RP && !Cfg::DKB_MERGED) {
 #pragma unroll
               for (int s = 0; s < 8; ++s)
                 umma_ss(tmem + Cfg::T_DKB, desc_at(mDS, po + mnmajor_step<128>(s)),
@@ -313,20 +329,22 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
             umma_commit(qdo_free + 8 * st);
           } else if (role == 2) {
-#pragma unroll
-            for (int s = 0; s < 8; ++s) {
-              if (Cfg::MERGE)
-                umma_ss(tmem + Cfg::T_DK, desc_at(mDS, po + mnmajor_step<128>(s)),
-                        desc_at(mQQb, so + mnmajor_step<D>(s)), idTM, (acc0 | (s > 0)) ? 1u : 0u);
-              else
-                umma_ss(tmem + Cfg::T_DK, desc_at(mDS, po + mnmajor_step<128>(s)),
-                        desc_at(mQ, so + mnmajor_step<D>(s)), idTD, (acc0 | (s > 0)) ? 1u : 0u);
-            }
-            if (NQ == 2) {  // dK += dS^T . lo(q*scale)
+            if (Cfg::MERGE_K) {  // dK(hi) | dK(lo) | dKb in one accumulator
 #pragma unroll
               for (int s = 0; s < 8; ++s)
                 umma_ss(tmem + Cfg::T_DK, desc_at(mDS, po + mnmajor_step<128>(s)),
-                        desc_at(mQ, so + Cfg::OFF_QLO + mnmajor_step<D>(s)), idTD, 1);
+                        desc_at(mQall, so + mnmajor_step<D>(s)), idKM, (acc0 | (s > 0)) ? 1u : 0u);
+            } else {
+#pragma unroll
+              for (int s = 0; s < 8; ++s)
+                umma_ss(tmem + Cfg::T_DK, desc_at(mDS, po + mnmajor_step<128>(s)),
+                        desc_at(mQ, so + mnmajor_step<D>(s)), idTD, (acc0 | (s > 0)) ? 1u : 0u);
+              if (NQ == 2) {  // dK += dS^T . lo(q*scale)
+#pragma unroll
+                for (int s = 0; s < 8; ++s)
+                  umma_ss(tmem + Cfg::T_DK, desc_at(mDS, po + mnmajor_step<128>(s)),
+                          desc_at(mQ, so + Cfg::OFF_QLO + mnmajor_step<D>(s)), idTD, 1);
+              }
             }
             umma_commit(qdo_free + 8 * st);
           } else {
@@ -338,7 +356,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
 #pragma unroll
             for (int s = 0; s < 8; ++s) {  // contraction over the 128 keys
-              if (Cfg::MERGE) {
+              if (Cfg::MERGE_Q) {
                 umma_ss(tq + Cfg::T_DQ, desc_at(kDS, po + kmajor_step<128>(s)), desc_at(mKKc, mnmajor_step<D>(s)),
                         idQM, s > 0);
               } else {
@@ -346,7 +364,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         idQD, s > 0);
                 if (RP)
                   umma_ss(tq + Cfg::T_DQB, desc_at(kDS, po + kmajor_step<128>(s)),
-                          desc_at(mKc, mnmajor_step<RPX>(s)), idQR, s > 0);
+                          desc_at(mKc, mnmajor_step<Cfg::RCX>(s)), idQC, s > 0);
               }
             }
             umma_commit(dq_full + 8 * qb);
@@ -439,7 +457,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           float* dstb = a.dqb_acc + (((int64_t)bq * a.Sq + grow) * a.Hq + hq) * a.R;
           const int used = 2 * a.R;  // (hi, lo) column groups of the centred factor
 #pragma unroll 1
-          for (int c0 = 0; c0 < RPX && c0 < used; c0 += 16) {
+          for (int c0 = 0; c0 < Cfg::RCX && c0 < used; c0 += 16) {
             uint32_t r[16];
             tmem_ld16(tq + Cfg::T_DQB + c0, r);
             tmem_wait_ld(r);
@@ -450,7 +468,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 if (c < a.R) {
                   float v = __uint_as_float(r[i]);
 #pragma unroll
-                  for (int g = 0; g < 4; ++g) v = fmaf(s_kbc[g * RPX + c], rsum[g], v);
+                  for (int g = 0; g < 4; ++g) v = fmaf(s_kbc[g * Cfg::RCX + c], rsum[g], v);
                   atomicAdd(dstb + c, v);
                 } else if (c < used) {
                   atomicAdd(dstb + c - a.R, __uint_as_float(r[i]));
@@ -477,8 +495,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       // k_bias of the four keys the centred copy refers to (one per 32-key group), as fp32; read by the drain
       // warpgroup, which is ordered after this through the first pds_ready -> dq_full chain
       const T* kb_bh = a.k_bias_t<T>() + (a.bk_bcast ? 0 : b) * a.kb_stride[0] + (a.hk_bcast ? 0 : h) * a.kb_stride[1];
-      for (int i = threadIdx.x; i < 4 * RPX; i += 256) {
-        const int g = i / RPX, c = i % RPX;
+      for (int i = threadIdx.x; i < 4 * Cfg::RCX; i += 256) {
+        const int g = i / Cfg::RCX, c = i % Cfg::RCX;
         s_kbc[i] = c < a.R ? to_f32(kb_bh[(int64_t)min(k0 + 32 * g + 16, a.Sk - 1) * a.kb_stride[2] + c]) : 0.f;
       }
     }
@@ -615,6 +633,13 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_ld16(tmem + Cfg::T_DK + lane_off + c0, rk);
         tmem_wait_ld(rv);
         tmem_wait_ld(rk);
+        if (Cfg::MERGE_K && NQ == 2) {  // the lo product of the split query sits 32 columns further
+          uint32_t rl[16];
+          tmem_ld16(tmem + Cfg::T_DK + 32 + lane_off + c0, rl);
+          tmem_wait_ld(rl);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) rk[i] = __float_as_uint(__uint_as_float(rk[i]) + __uint_as_float(rl[i]));
+        }
         if (krow < a.Sk) {
 #pragma unroll
           for (int g = 0; g < 2; ++g) {
@@ -730,7 +755,7 @@ static BwdWs bwd_layout(const fb_params* p, const PackPlan& plan) {
   w.off_qpack = 0;
   w.off_kpack = plan.q_bytes;
   w.off_kcenter = w.off_kpack + plan.k_bytes;
-  w.off_qs = w.off_kcenter + plan.k_bytes;
+  w.off_qs = w.off_kcenter + plan.kc_bytes;
   w.off_dq = w.off_qs + plan.qs_bytes;
   // query rows padded to whole tiles: the bulk reductions of the backward write whole [128][D] tiles
   const size_t dq = round256((size_t)p->B * ((p->Sq + 127) / 128) * 128 * p->H * p->D * 4);
@@ -743,14 +768,23 @@ static BwdWs bwd_layout(const fb_params* p, const PackPlan& plan) {
   return w;
 }
 
+// the variants launch_bwd_sm100 can dispatch to, and whether their tiles fit one SM
+static bool bwd_cfg_fits(int D, int RP, int nq) {
+#define FB_FIT(DD, RR) \
+  if (D == DD && RP == RR) return nq == 2 ? BwdCfg<DD, RR, 2>::FITS : BwdCfg<DD, RR, 1>::FITS;
+  FB_FIT(32, 0) FB_FIT(32, 16) FB_FIT(32, 32) FB_FIT(32, 64)
+  FB_FIT(64, 0) FB_FIT(64, 16) FB_FIT(64, 32)
+#undef FB_FIT
+  return false;
+}
+
 bool bwd_sm100_supported(const fb_params* p, PackPlan* plan) {
   if (p->flags & FB_FLAG_FORCE_GENERAL) return false;
   if (p->mask_kind != FB_MASK_NONE) return false;
   if (!(p->D == 32 || p->D == 64)) return false;
   if (!(p->softmax_scale > 0.f) || !isfinite(p->softmax_scale)) return false;
   if (!plan_pack(p, plan, true)) return false;
-  if (256 + 3 * p->D + 2 * plan->RP > 512) return false;
-  if (p->D == 64 && plan->RP == 32 && plan->nq == 2) return false;  // tiles exceed the shared memory of an SM
+  if (!bwd_cfg_fits(p->D, plan->RP, plan->nq)) return false;  // shared or tensor memory of an SM exceeded
   if (!tma_compatible(p->q, p->q_stride[2], p->q_stride[1], p->q_stride[0], p->H, p->B)) return false;
   if (!tma_compatible(p->k, p->k_stride[2], p->k_stride[1], p->k_stride[0], p->H, p->B)) return false;
   if (!tma_compatible(p->v, p->v_stride[2], p->v_stride[1], p->v_stride[0], p->H, p->B)) return false;
@@ -808,8 +842,9 @@ static int launch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t s
     if ((rc = make_tmap_4d(&tKb, kpack, RP, p->Sk, plan.Hk, plan.Bk, RP, (int64_t)RP * p->Sk,
                            (int64_t)RP * p->Sk * plan.Hk, RP, 128)))
       return rc;
-    if ((rc = make_tmap_4d(&tKc, kcenter, RP, p->Sk, plan.Hk, plan.Bk, RP, (int64_t)RP * p->Sk,
-                           (int64_t)RP * p->Sk * plan.Hk, RP, 128)))
+    constexpr int RC = Cfg::RCX;
+    if ((rc = make_tmap_4d(&tKc, kcenter, RC, p->Sk, plan.Hk, plan.Bk, RC, (int64_t)RC * p->Sk,
+                           (int64_t)RC * p->Sk * plan.Hk, RC, 128)))
       return rc;
   } else {
     tQb = tQ;

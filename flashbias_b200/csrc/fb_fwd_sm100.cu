@@ -64,6 +64,15 @@ __device__ __forceinline__ void tma_tile_4d(uint32_t dst, const CUtensorMap* m, 
   for (int blk = 0; blk < NB; ++blk) tma_load_4d(dst + blk * 128 * SWB, m, bar, col0 + blk * (SWB / 2), row0, h, b);
 }
 
+// Development aid, compiled only with -DFB_TRACE: CTA 0 records clock64() at phase boundaries, 16 slots per key tile.
+#ifdef FB_TRACE
+__device__ long long g_fwd_trace[64 * 16];
+#define FB_TRACE_MARK(j, slot) \
+  do { if (blockIdx.x == 0 && (j) < 64) g_fwd_trace[(j) * 16 + (slot)] = clock64(); } while (0)
+#else
+#define FB_TRACE_MARK(j, slot) do { } while (0)
+#endif
+
 template <typename T, int D, int RP, int NQ>
 __global__ void __launch_bounds__(224, FwdCfg<D, RP, NQ>::MINB)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -187,7 +196,9 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           mbar_wait(s_read, (j - 1) & 1, abort_flag, a.status);
           tc_fence_after_sync();
         }
+        FB_TRACE_MARK(j, 8);
         issue_S(j);
+        FB_TRACE_MARK(j, 9);
       }
     }
   } else if (warp == 6) {
@@ -202,12 +213,14 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         mbar_wait(v_full + 8 * vs, (j / VST) & 1, abort_flag, a.status);
         mbar_wait(p_ready, j & 1, abort_flag, a.status);
         tc_fence_after_sync();
+        FB_TRACE_MARK(j, 10);
         const uint32_t vo = vs * Cfg::Q_BYTES;
 #pragma unroll
         for (int s = 0; s < 8; ++s)
           umma_ts(tO, tP + s * 8, desc_at(dV, vo + mnmajor_step<D>(s)), idO, (j > 0 || s > 0) ? 1u : 0u);
         umma_commit(pv_done);
         umma_commit(v_free + 8 * vs);
+        FB_TRACE_MARK(j, 11);
       }
     }
   } else {
@@ -220,8 +233,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     uint32_t ra[32], rb[32];  // two register buffers: the TMEM load of one chunk overlaps the math of the other
     for (int j = 0; j < n_kv; ++j) {
       const int k0 = j * 128;
+      if (threadIdx.x == 0) FB_TRACE_MARK(j, 0);
       mbar_wait(s_full, j & 1, abort_flag, a.status);
       tc_fence_after_sync();
+      if (threadIdx.x == 0) FB_TRACE_MARK(j, 1);
       const bool need_mask = (a.causal && k0 + 127 > q0) || (k0 + 128 > a.Sk);
       const uint32_t tSl = tS + lane_off;
       // ---- pass 1: row maximum (four independent chains)
@@ -253,9 +268,11 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tmem_ld32(tSl, ra);  // first chunk of pass 2
       chunk_max(rb, 3);
       const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])));
+      if (threadIdx.x == 0) FB_TRACE_MARK(j, 2);
       if (j > 0) {
         mbar_wait(pv_done, (j - 1) & 1, abort_flag, a.status);  // P buffer free, O stable
         tc_fence_after_sync();
+        if (threadIdx.x == 0) FB_TRACE_MARK(j, 3);
         const bool grow_needed = (m_new - m_used) * sl2 > 8.f;
         if (__any_sync(0xffffffffu, grow_needed)) {
           const float alpha = m_new == -INFINITY ? 1.f : fast_exp2((m_used - m_new) * sl2);
@@ -312,11 +329,13 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       chunk_exp(ra, 2);
       tmem_wait_ld(rb);
       tc_fence_before_sync();
+      if (threadIdx.x == 0) FB_TRACE_MARK(j, 4);
       mbar_arrive_warp(s_read);  // S is in registers: the tensor core may start on the next key tile
       chunk_exp(rb, 3);
       l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       tmem_wait_st();
       tc_fence_before_sync();
+      if (threadIdx.x == 0) FB_TRACE_MARK(j, 5);
       mbar_arrive_warp(p_ready);
     }
     // ---- epilogue: O / l -> global, lse
@@ -356,6 +375,13 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 // ------------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------------
+#ifdef FB_TRACE
+}  // namespace fb
+extern "C" int fb_debug_trace_fwd(long long* out, int n) {
+  return (int)cudaMemcpyFromSymbol(out, fb::g_fwd_trace, sizeof(long long) * (n < 1024 ? n : 1024));
+}
+namespace fb {
+#endif
 static bool o_store_ok(const fb_params* p) {
   if (reinterpret_cast<uintptr_t>(p->o) & 15) return false;
   for (int i = 0; i < 3; ++i)

@@ -31,12 +31,14 @@ struct PackPlan {
   int nq;          // 1 or 2 query terms
   float qb_mult;   // multiplier applied to q_bias when packing (1/scale when nq == 1)
   int RP;          // packed factor width: 0 (no bias), 16, 32 or 64
+  int RC;          // width of the centred k-side copy of the backward (>= RP; 32 beside a head_dim-32 K tile)
   int Bq, Hq, Bk, Hk;
-  size_t q_bytes, k_bytes, qs_bytes;  // packed q factor, packed k factor, scaled-query copy (each rounded to 256)
+  size_t q_bytes, k_bytes, kc_bytes, qs_bytes;  // packed q factor, packed k factor, centred k factor, scaled-query
+                                               // copy (each rounded to 256)
 };
 // false if the rank does not fit the tensor path; for_bwd reserves room for the centred (hi, lo) k-side copy
 bool plan_pack(const fb_params* p, PackPlan* plan, bool for_bwd = false);
-// kcenter (optional, same layout as kpack): k_bias minus the k_bias of the middle key of each group of 32 keys.
+// kcenter (optional, rows of plan.RC columns): k_bias minus the k_bias of the middle key of each group of 32 keys.
 int launch_pack(const fb_params* p, const PackPlan& plan, void* qpack, void* kpack, void* kcenter, cudaStream_t st);
 int launch_pack_qscaled(const fb_params* p, const PackPlan& plan, void* qs, cudaStream_t st);
 

@@ -32,6 +32,8 @@ bool plan_pack(const fb_params* p, PackPlan* plan, bool for_bwd) {
   plan->nq = pow2 ? 1 : 2;
   plan->qb_mult = pow2 ? (float)(1.0 / (double)p->softmax_scale) : 1.f;
   plan->qs_bytes = pow2 ? 0 : round256((size_t)p->B * p->H * p->Sq * 2 * p->D * 2);
+  plan->RC = 0;
+  plan->kc_bytes = 0;
   if (p->R <= 0) {
     plan->RP = 0;
     plan->q_bytes = plan->k_bytes = 0;
@@ -42,12 +44,17 @@ bool plan_pack(const fb_params* p, PackPlan* plan, bool for_bwd) {
   if (plan->RP > 64) return false;
   plan->q_bytes = round256((size_t)plan->Bq * plan->Hq * p->Sq * plan->RP * 2);
   plan->k_bytes = round256((size_t)plan->Bk * plan->Hk * p->Sk * plan->RP * 2);
+  if (for_bwd) {
+    // beside a head_dim-32 K tile the centred copy is 32 columns wide: [K | Kc] then reads as one MMA operand
+    plan->RC = (p->D == 32 && plan->RP < 32) ? 32 : plan->RP;
+    plan->kc_bytes = round256((size_t)plan->Bk * plan->Hk * p->Sk * plan->RC * 2);
+  }
   return true;
 }
 
 template <typename T>
 __global__ void __launch_bounds__(256) pack_factor_kernel(const T* __restrict__ src, int64_t sb, int64_t sh, int64_t ss,
-                                                          int Bx, int Hx, int S, int R, int RP, float mult,
+                                                          int Bx, int Hx, int S, int R, int RP, int RC, float mult,
                                                           T* __restrict__ dst, T* __restrict__ dst_centered,
                                                           int* status) {
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // (b, h, s)
@@ -74,8 +81,8 @@ __global__ void __launch_bounds__(256) pack_factor_kernel(const T* __restrict__ 
     int s0 = (s & ~31) + 16;
     if (s0 > S - 1) s0 = S - 1;
     const T* in0 = src + b * sb + h * sh + (int64_t)s0 * ss;
-    T* outc = dst_centered + idx * RP;
-    for (int c = 2 * R; c < RP; ++c) outc[c] = from_f32<T>(0.f);
+    T* outc = dst_centered + idx * RC;
+    for (int c = 2 * R; c < RC; ++c) outc[c] = from_f32<T>(0.f);
     for (int c = 0; c < R; ++c) {  // two-term split: columns [0,R) hi, [R,2R) lo
       const float x = to_f32(in[c]) - to_f32(in0[c]);
       const T hi = from_f32<T>(x);
@@ -121,10 +128,10 @@ static int launch_pack_t(const fb_params* p, const PackPlan& plan, void* qpack, 
   const int64_t nq = (int64_t)plan.Bq * plan.Hq * p->Sq, nk = (int64_t)plan.Bk * plan.Hk * p->Sk;
   pack_factor_kernel<T><<<(unsigned)((nq + 255) / 256), 256, 0, st>>>(
       reinterpret_cast<const T*>(p->q_bias), p->q_bias_stride[0], p->q_bias_stride[1], p->q_bias_stride[2], plan.Bq,
-      plan.Hq, p->Sq, p->R, plan.RP, plan.qb_mult, reinterpret_cast<T*>(qpack), nullptr, p->status);
+      plan.Hq, p->Sq, p->R, plan.RP, plan.RC, plan.qb_mult, reinterpret_cast<T*>(qpack), nullptr, p->status);
   pack_factor_kernel<T><<<(unsigned)((nk + 255) / 256), 256, 0, st>>>(
       reinterpret_cast<const T*>(p->k_bias), p->k_bias_stride[0], p->k_bias_stride[1], p->k_bias_stride[2], plan.Bk,
-      plan.Hk, p->Sk, p->R, plan.RP, 1.f, reinterpret_cast<T*>(kpack), reinterpret_cast<T*>(kcenter), p->status);
+      plan.Hk, p->Sk, p->R, plan.RP, plan.RC, 1.f, reinterpret_cast<T*>(kpack), reinterpret_cast<T*>(kcenter), p->status);
   note_launch(2);
   return (int)cudaGetLastError();
 }
