@@ -146,7 +146,7 @@ __host__ __device__ __forceinline__ int dq_stage_off(int r, int ch) {
 }
 
 template <typename T, int D, int RP, int NQ>
-__global__ void __launch_bounds__(544, 1)
+__global__ void __launch_bounds__(512, 1)
 bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                  const __grid_constant__ CUtensorMap tmQb, const __grid_constant__ CUtensorMap tmKb,
@@ -197,7 +197,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         mbar_init(pds_free + 8 * i, 3);  // dV, dK and dQ chains read a P/dS buffer
         mbar_init(dq_full + 8 * i, 1);
         mbar_init(dq_drained + 8 * i, 4);  // the drain warps
-        mbar_init(pds_ready + 8 * i, 8);   // the compute warps  // alternating by query tile: the four issuers wait at different times
+        mbar_init(pds_ready + 8 * i, 8);   // the compute warps; alternating by query tile, as the issuers wait at
+                                           // different times
         mbar_init(stg_free + 8 * i, 1);  // the drain thread that issued the bulk reduction
       }
       mbar_fence_init();
@@ -211,6 +212,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
 
+  // 512 threads start with 128 registers each; the two compute warpgroups hold a whole tile of S and dP in
+  // registers and take 176, the drain warpgroup and the producer/issuer warpgroup keep 80.  Each warpgroup
+  // changes its budget at the head of its own branch.
+  if (warp >= 12) {
+  setmaxnreg_dec<80>();
   if (warp == 12) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0 && n_it > 0) {
@@ -221,36 +227,92 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (RP) tma_tile_bwd<RPX>(sKb, &tmKb, kv_full, k0, hk, bk);
       if (RP) tma_tile_bwd<Cfg::RCX>(sKc, &tmKc, kv_full, k0, hk, bk);
       tma_tile_bwd<D>(sV, &tmV, kv_full, k0, h, b);
-      for (int it = 0; it < n_it; ++it) {
+      auto load_tile = [&](int it) {
         const int st = it & 1;
         const uint32_t base = sStage + st * Cfg::STAGE_BYTES;
-        if (it >= 2) mbar_wait(qdo_free + 8 * st, ((it >> 1) - 1) & 1, abort_flag, a.status);
         mbar_expect_tx(qdo_full + 8 * st, Cfg::STAGE_BYTES);
         const int q0 = (i_begin + it) * 128;
         tma_tile_bwd<D>(base, &tmQ, qdo_full + 8 * st, q0, h, b);
         if (NQ == 2) tma_tile_bwd<D>(base + Cfg::OFF_QLO, &tmQ, qdo_full + 8 * st, q0, h, b, D);
         if (RP) tma_tile_bwd<RPX>(base + Cfg::OFF_QB, &tmQb, qdo_full + 8 * st, q0, hq, bq);
         tma_tile_bwd<D>(base + Cfg::OFF_DO, &tmDO, qdo_full + 8 * st, q0, h, b);
+      };
+      load_tile(0);
+      if (n_it > 1) load_tile(1);
+      // The same thread issues the dQ | dQb products: they become due when a query tile's P/dS are written,
+      // the next load when the other chains have finished with that tile's stage -- in this order, every tile.
+      constexpr uint32_t idQD = instr_desc(kBf16, false, true, 128, D);             // dQ: A K-major, B MN-major
+      constexpr uint32_t idQM = instr_desc(kBf16, false, true, 128, D + Cfg::RCX);  // dQ|dQb merged
+      constexpr uint32_t idQC = instr_desc(kBf16, false, true, 128, Cfg::RCX);      // dQb alone
+      const DescBase kDS = kmajor_base<128>(sPDS + tile_bytes(128)), mK = mnmajor_base<D>(sK),
+                     mKc = mnmajor_base<Cfg::RCX>(sKc);
+      const uint64_t dKKc = smem_desc(sK, Cfg::OFF_KC - Cfg::OFF_K, 8 * 64, 64);  // [K | Kc], 32-column blocks
+      const DescBase mKKc{(uint32_t)dKKc, (uint32_t)(dKKc >> 32)};
+      mbar_wait(kv_full, 0, abort_flag, a.status);
+      auto issue_dQ = [&](int it) {
+        const int buf = Cfg::PIPE ? (it & 1) : 0;
+        const uint32_t po = buf * Cfg::PDS_BYTES;
+        const int qb = it % Cfg::NDQ;  // dQ|dQb accumulator of this tile
+        const uint32_t tq = tmem + qb * Cfg::DQ_STRIDE;
+        mbar_wait(pds_ready + 8 * (it & 1), (it >> 1) & 1, abort_flag, a.status);
+        if (it >= Cfg::NDQ)  // the drain warpgroup has read the tile that used this accumulator last
+          mbar_wait(dq_drained + 8 * qb, (it / Cfg::NDQ - 1) & 1, abort_flag, a.status);
+        tc_fence_after_sync();
+        FB_TRACE_MARK(it, 10);
+        if (!FB_DBG(4)) {
+#pragma unroll
+          for (int s = 0; s < 8; ++s) {  // contraction over the 128 keys
+            if (Cfg::MERGE_Q) {
+              umma_ss(tq + Cfg::T_DQ, desc_at(kDS, po + kmajor_step<128>(s)), desc_at(mKKc, mnmajor_step<D>(s)),
+                      idQM, s > 0);
+            } else {
+              umma_ss(tq + Cfg::T_DQ, desc_at(kDS, po + kmajor_step<128>(s)), desc_at(mK, mnmajor_step<D>(s)),
+                      idQD, s > 0);
+              if (RP)
+                umma_ss(tq + Cfg::T_DQB, desc_at(kDS, po + kmajor_step<128>(s)),
+                        desc_at(mKc, mnmajor_step<Cfg::RCX>(s)), idQC, s > 0);
+            }
+          }
+        }
+        umma_commit(dq_full + 8 * qb);
+        umma_commit(pds_free + 8 * buf);  // this chain no longer reads the P/dS buffer of the tile
+        FB_TRACE_MARK(it, 11);
+      };
+#pragma unroll 1
+      for (int it = 0; it < n_it; ++it) {
+        issue_dQ(it);
+        if (it + 2 < n_it) {  // the S|dP, dV and dK chains have finished reading the stage of tile it
+          mbar_wait(qdo_free + 8 * (it & 1), (it >> 1) & 1, abort_flag, a.status);
+          load_tile(it + 2);
+        }
       }
+      umma_commit(all_done);
     }
   } else if (warp >= 13) {
     // ------------------------------------------------------------------ MMA issuers
-    // Four warps, one elected thread each, one per warp scheduler.  A thread that issues tcgen05.mma gets an
-    // issue slot only when the compute warps of its scheduler stall, so one thread alone cannot feed the tensor
-    // core; the chains below are independent (different accumulators) and run concurrently:
-    //   role 0  S and dP of the next query tile      role 1  dV (and dKb when it is a separate accumulator)
-    //   role 2  dK (or dK|dKb merged)                role 3  dQ | dQb
+    // One elected thread per warp, each warp on its own warp scheduler (the producer warp issues the fourth
+    // chain, dQ | dQb).  A thread that issues tcgen05.mma competes with the compute warps of its scheduler, so
+    // one thread alone cannot feed the tensor core; the chains are independent (different accumulators) and
+    // run concurrently:
+    //   warp 13  S and dP of query tile i, as soon as tile i-1 is in registers
+    //   warp 14  dV (and dKb when it is a separate accumulator)
+    //   warp 15  dK (or dK(hi) | dK(lo) | dKb merged)
     // Every accumulator is only ever touched by one thread, which keeps its MMAs ordered.
     if (lane == 0 && n_it > 0) {
       const int role = warp - 13;
       constexpr uint32_t idS = instr_desc(kBf16, false, false, 128, 128);  // S, dP: both operands K-major
       constexpr uint32_t idTD = instr_desc(kBf16, true, true, 128, D);     // dV, dK: A^T (MN-major), B MN-major
       constexpr uint32_t idTR = instr_desc(kBf16, true, true, 128, RPX);   // dKb
-      constexpr uint32_t idQD = instr_desc(kBf16, false, true, 128, D);    // dQ: A K-major, B MN-major
+      constexpr uint32_t idKM = instr_desc(kBf16, true, true, 128, Cfg::MERGE_K ? 32 * Cfg::KBLK : 32);  // merged dK
+      // descriptor views built once (stage 0 / buffer 0); each MMA adds a constant to the address field
+      const DescBase mP = mnmajor_base<128>(sPDS), mDS = mnmajor_base<128>(sPDS + tile_bytes(128));
+      // merged views (head_dim 32): 32-column blocks of 64-byte-swizzled rows, the next block found at a
+      // leading-dimension offset of the distance between the tiles
+      const uint64_t dQall = smem_desc(sStage, Cfg::D_BYTES, 8 * 64, 64);
+      const DescBase mQall{(uint32_t)dQall, (uint32_t)(dQall >> 32)};
       mbar_wait(kv_full, 0, abort_flag, a.status);
       tc_fence_after_sync();
       if (role == 0) {
-        // descriptor views built once (stage 0); each MMA adds a constant to the address field
         const DescBase kQ = kmajor_base<D>(sStage), kDO = kmajor_base<D>(sStage + Cfg::OFF_DO),
                        kQb = kmajor_base<RPX>(sStage + Cfg::OFF_QB), kK = kmajor_base<D>(sK),
                        kKb = kmajor_base<RPX>(sKb), kV = kmajor_base<D>(sV);
@@ -290,18 +352,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       } else {
         const DescBase mQ = mnmajor_base<D>(sStage), mDO = mnmajor_base<D>(sStage + Cfg::OFF_DO),
-                       mQb = mnmajor_base<RPX>(sStage + Cfg::OFF_QB), mK = mnmajor_base<D>(sK),
-                       mKc = mnmajor_base<Cfg::RCX>(sKc), mP = mnmajor_base<128>(sPDS),
-                       mDS = mnmajor_base<128>(sPDS + tile_bytes(128)),
-                       kDS = kmajor_base<128>(sPDS + tile_bytes(128));
-        // merged views (head_dim 32): 32-column blocks of 64-byte-swizzled rows, the next block found at a
-        // leading-dimension offset of the distance between the tiles
-        const uint64_t dQall = smem_desc(sStage, Cfg::D_BYTES, 8 * 64, 64);
-        const uint64_t dKKc = smem_desc(sK, Cfg::OFF_KC - Cfg::OFF_K, 8 * 64, 64);
-        const DescBase mQall{(uint32_t)dQall, (uint32_t)(dQall >> 32)}, mKKc{(uint32_t)dKKc, (uint32_t)(dKKc >> 32)};
-        constexpr uint32_t idKM = instr_desc(kBf16, true, true, 128, Cfg::MERGE_K ? 32 * Cfg::KBLK : 32);  // merged dK
-        constexpr uint32_t idQM = instr_desc(kBf16, false, true, 128, D + Cfg::RCX);                       // dQ|dQb
-        constexpr uint32_t idQC = instr_desc(kBf16, false, true, 128, Cfg::RCX);                           // dQb alone
+                       mQb = mnmajor_base<RPX>(sStage + Cfg::OFF_QB);
 #pragma unroll 1
         for (int it = 0; it < n_it; ++it) {
           const int st = it & 1;
@@ -309,13 +360,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           const int buf = Cfg::PIPE ? st : 0;
           const uint32_t po = buf * Cfg::PDS_BYTES;
           const uint32_t acc0 = it > 0 ? 1u : 0u;
-          if (role != 3) mbar_wait(qdo_full + 8 * st, (it >> 1) & 1, abort_flag, a.status);
+          mbar_wait(qdo_full + 8 * st, (it >> 1) & 1, abort_flag, a.status);
           mbar_wait(pds_ready + 8 * (it & 1), (it >> 1) & 1, abort_flag, a.status);
           tc_fence_after_sync();
           FB_TRACE_MARK(it, 4 + 2 * role);
           if (FB_DBG(4)) {
-            if (role != 3) umma_commit(qdo_free + 8 * st);
-            if (role == 3) umma_commit(dq_full + 8 * (it % Cfg::NDQ));
           } else if (role == 1) {
 #pragma unroll
             for (int s = 0; s < 8; ++s)  // contraction over the 128 query rows
@@ -327,55 +376,33 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 umma_ss(tmem + Cfg::T_DKB, desc_at(mDS, po + mnmajor_step<128>(s)),
                         desc_at(mQb, so + mnmajor_step<RPX>(s)), idTR, (acc0 | (s > 0)) ? 1u : 0u);
             }
-            umma_commit(qdo_free + 8 * st);
-          } else if (role == 2) {
-            if (Cfg::MERGE_K) {  // dK(hi) | dK(lo) | dKb in one accumulator
+          } else if (Cfg::MERGE_K) {  // dK(hi) | dK(lo) | dKb in one accumulator
 #pragma unroll
-              for (int s = 0; s < 8; ++s)
-                umma_ss(tmem + Cfg::T_DK, desc_at(mDS, po + mnmajor_step<128>(s)),
-                        desc_at(mQall, so + mnmajor_step<D>(s)), idKM, (acc0 | (s > 0)) ? 1u : 0u);
-            } else {
-#pragma unroll
-              for (int s = 0; s < 8; ++s)
-                umma_ss(tmem + Cfg::T_DK, desc_at(mDS, po + mnmajor_step<128>(s)),
-                        desc_at(mQ, so + mnmajor_step<D>(s)), idTD, (acc0 | (s > 0)) ? 1u : 0u);
-              if (NQ == 2) {  // dK += dS^T . lo(q*scale)
-#pragma unroll
-                for (int s = 0; s < 8; ++s)
-                  umma_ss(tmem + Cfg::T_DK, desc_at(mDS, po + mnmajor_step<128>(s)),
-                          desc_at(mQ, so + Cfg::OFF_QLO + mnmajor_step<D>(s)), idTD, 1);
-              }
-            }
-            umma_commit(qdo_free + 8 * st);
+            for (int s = 0; s < 8; ++s)
+              umma_ss(tmem + Cfg::T_DK, desc_at(mDS, po + mnmajor_step<128>(s)),
+                      desc_at(mQall, so + mnmajor_step<D>(s)), idKM, (acc0 | (s > 0)) ? 1u : 0u);
           } else {
-            const int qb = it % Cfg::NDQ;  // dQ|dQb accumulator of this tile
-            const uint32_t tq = tmem + qb * Cfg::DQ_STRIDE;
-            if (it >= Cfg::NDQ) {  // the drain warpgroup has read the tile that used this accumulator last
-              mbar_wait(dq_drained + 8 * qb, (it / Cfg::NDQ - 1) & 1, abort_flag, a.status);
-              tc_fence_after_sync();
-            }
 #pragma unroll
-            for (int s = 0; s < 8; ++s) {  // contraction over the 128 keys
-              if (Cfg::MERGE_Q) {
-                umma_ss(tq + Cfg::T_DQ, desc_at(kDS, po + kmajor_step<128>(s)), desc_at(mKKc, mnmajor_step<D>(s)),
-                        idQM, s > 0);
-              } else {
-                umma_ss(tq + Cfg::T_DQ, desc_at(kDS, po + kmajor_step<128>(s)), desc_at(mK, mnmajor_step<D>(s)),
-                        idQD, s > 0);
-                if (RP)
-                  umma_ss(tq + Cfg::T_DQB, desc_at(kDS, po + kmajor_step<128>(s)),
-                          desc_at(mKc, mnmajor_step<Cfg::RCX>(s)), idQC, s > 0);
-              }
+            for (int s = 0; s < 8; ++s)
+              umma_ss(tmem + Cfg::T_DK, desc_at(mDS, po + mnmajor_step<128>(s)),
+                      desc_at(mQ, so + mnmajor_step<D>(s)), idTD, (acc0 | (s > 0)) ? 1u : 0u);
+            if (NQ == 2) {  // dK += dS^T . lo(q*scale)
+#pragma unroll
+              for (int s = 0; s < 8; ++s)
+                umma_ss(tmem + Cfg::T_DK, desc_at(mDS, po + mnmajor_step<128>(s)),
+                        desc_at(mQ, so + Cfg::OFF_QLO + mnmajor_step<D>(s)), idTD, 1);
             }
-            umma_commit(dq_full + 8 * qb);
           }
+          umma_commit(qdo_free + 8 * st);
           umma_commit(pds_free + 8 * buf);  // this chain no longer reads the P/dS buffer of the tile
           FB_TRACE_MARK(it, 5 + 2 * role);
         }
       }
       umma_commit(all_done);  // every MMA of this thread
     }
-  } else if (warp >= 8 && warp < 12) {
+  }
+  } else if (warp >= 8) {
+    setmaxnreg_dec<80>();
     // ------------------------------------------------------------------ drain warpgroup
     // dQ | dQb of each query tile from TMEM into the fp32 accumulators in global memory, off the critical path
     // of the warps that compute P and dS.  One thread per query row.
@@ -485,6 +512,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else if (n_it > 0) {
     // ------------------------------------------------------------------ compute warpgroups (warps 0-7)
+    setmaxnreg_inc<176>();
     const int wg = warp >> 2;
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
@@ -522,15 +550,29 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int grow = q0 + row;
       // a row that saw no key has lse = -inf: make its probabilities exactly zero
       const float lse2_cur = lse_raw == -INFINITY ? INFINITY : lse_raw * kLog2e, dlt_cur = dlt;
-      if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 17);
-      load_row_stats(it + 1, lse_raw, dlt);  // next tile's statistics: the loads complete under this tile's math
-      if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 18);
       const uint32_t sP_cur = sPDS + (Cfg::PIPE ? (it & 1) : 0) * Cfg::PDS_BYTES;  // P tile, dS tile behind it
       const bool need_mask = (a.causal && k0 + 127 > q0) || (k0 + 128 > a.Sk);
       float ds_sum0 = 0.f, ds_sum1 = 0.f;  // fp32 row sums of dS over this thread's two 32-column groups
       if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 14);
       mbar_wait(s_full, it & 1, abort_flag, a.status);
       mbar_wait(dp_full, it & 1, abort_flag, a.status);
+      tc_fence_after_sync();
+      if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 0);
+      // The thread's 64 columns of S and of dP go to registers at once; tensor memory is then free for S and dP
+      // of the next query tile, which the tensor core computes under this tile's arithmetic.
+      uint32_t rs0[32], rd0[32], rs1[32], rd1[32];
+      const uint32_t tSl = tmem + Cfg::T_S + lane_off + wg * 64, tDl = tmem + Cfg::T_DP + lane_off + wg * 64;
+      tmem_ld32(tSl, rs0);
+      tmem_ld32(tDl, rd0);
+      tmem_ld32(tSl + 32, rs1);
+      tmem_ld32(tDl + 32, rd1);
+      tmem_wait_ld(rs0);
+      tmem_wait_ld(rd0);
+      tmem_wait_ld(rs1);
+      tmem_wait_ld(rd1);
+      tc_fence_before_sync();
+      mbar_arrive_warp(sdp_read);
+      if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 2);
       // the MMAs that read this P/dS buffer last (query tile it - NBUF) have completed
       if (it >= Cfg::NBUF) {
         if (Cfg::PIPE) {
@@ -540,9 +582,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           mbar_wait(pds_free, (it - 1) & 1, abort_flag, a.status);
         }
       }
-      tc_fence_after_sync();
-      if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 0);
-      uint32_t rs0[32], rd0[32];
+      if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 3);
       auto chunk = [&](uint32_t (&rs)[32], uint32_t (&rd)[32], int c) {
         const int col0 = wg * 64 + c * 32;
         float sum0 = 0.f, sum1 = 0.f;
@@ -580,29 +620,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         return sum0 + sum1;
       };
-      const uint32_t tSl = tmem + Cfg::T_S + lane_off + wg * 64, tDl = tmem + Cfg::T_DP + lane_off + wg * 64;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        tmem_ld32(tSl + c * 32, rs0);
-        tmem_ld32(tDl + c * 32, rd0);
-        tmem_wait_ld(rs0);
-        tmem_wait_ld(rd0);
-        if (c == 1) {  // S and dP are in registers: the tensor core may overwrite them with the next tile's
-          tc_fence_before_sync();
-          mbar_arrive_warp(sdp_read);
-        }
-        if (FB_DBG(32)) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            rs0[i] = 0u;
-            rd0[i] = 0u;
-          }
-        }
-        if (lane == 0 && warp == 0) FB_TRACE_MARK(it, c == 0 ? 2 : 15);
-        const float sum = chunk(rs0, rd0, c);
-        if (lane == 0 && warp == 0 && c == 0) FB_TRACE_MARK(it, 3);
-        if (c == 0) ds_sum0 = sum; else ds_sum1 = sum;
-      }
+      ds_sum0 = chunk(rs0, rd0, 0);
+      if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 15);
+      load_row_stats(it + 1, lse_raw, dlt);  // next tile's statistics: the loads complete under this tile's math
+      if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 17);
+      ds_sum1 = chunk(rs1, rd1, 1);
       if (RP) {
         // four buffers: the drain warpgroup may lag up to three query tiles behind
         float* s_rowsum = reinterpret_cast<float*>(smem + Cfg::OFF_ROWSUM) + (it & 3) * 512;
@@ -674,7 +696,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
     }
-  } else if (warp < 8) {
+  } else {
     // causal with Sq < Sk: these keys are seen by no query; their gradients are zero
     const int wg = warp >> 2;
     const int row = (warp & 3) * 32 + lane;
@@ -892,7 +914,7 @@ static int launch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t s
   }
   const unsigned grid = (unsigned)((int64_t)a.nk_tiles * p->B * p->H);
   prof_before(KC_BWD_MAIN, st);
-  kern<<<grid, 544, Cfg::SMEM, st>>>(tQ, tK, tV, tDO, tQb, tKb, tKc, a);
+  kern<<<grid, 512, Cfg::SMEM, st>>>(tQ, tK, tV, tDO, tQb, tKb, tKc, a);
   prof_after(KC_BWD_MAIN, st);
   note_launch();
   if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
