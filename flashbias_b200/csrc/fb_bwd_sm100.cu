@@ -29,13 +29,14 @@ struct BwdArgs {
   int B, H, Sq, Sk, nq_tiles, nk_tiles, causal, R;
   int hq_bcast, bq_bcast, hk_bcast, bk_bcast;
   int Hq, Hk;  // head extents of the un-expanded factors
-  float dk_scale;    // applied to dK and dk_bias on store: the softmax scale unless it is already in the operands
+  float dk_scale;    // applied to dK on store
+  float dkb_scale;   // applied to dk_bias on store
   float scale_log2;  // logits * log2(e) = S * scale_log2
   const float* lse;
   const float* delta;
   int64_t lse_stride_bh;
   float* dq_acc;   // (B, Sq, H, D) fp32
-  float* dqb_acc;  // (Bq, Sq, Hq, R) fp32
+  float* dqb_acc;  // (Bq, Hq, nq_tiles * 128, R) fp32
   float* dkb_acc;  // (Bk, Sk, Hk, R) fp32
   void* dk;
   void* dv;
@@ -57,40 +58,48 @@ struct BwdCfg {
   static constexpr int RC = RP ? ((D == 32 && RP < 32) ? 32 : RP) : 0;
   static constexpr int RCX = RC ? RC : 16;
   static constexpr int RC_BYTES = RC ? tile_bytes(RCX) : 0;
-  // one stage: the query terms (q, or hi then lo of q*scale), Qb, dO
-  static constexpr int OFF_QLO = D_BYTES;
-  static constexpr int OFF_QB = NQ * D_BYTES;
+  // one stage of the query-tile ring: Q, Qb, dO
+  static constexpr int OFF_QB = D_BYTES;
   static constexpr int OFF_DO = OFF_QB + R_BYTES;
   static constexpr int STAGE_BYTES = OFF_DO + D_BYTES;
-  static constexpr int PDS_BYTES = 2 * tile_bytes(128);  // P then dS
-  // Operands that share the A tile are read as ONE MN-major B operand of several 32-column blocks (head_dim 32:
+  static constexpr int TILE128 = tile_bytes(128);  // one P or dS tile
+  // Operands that share the A tile are read as ONE MN-major B operand of two 32-column blocks (head_dim 32:
   // 64-byte-swizzled tiles at a constant distance), which saves the repeated shared-memory fetch of A:
-  //   dK chain:  dS^T . [q hi | q lo | Qb]   (Qb only when it is 32 columns wide)
-  //   dQ chain:  dS   . [K | Kc]
-  static constexpr int KBLK = (D == 32) ? NQ + (RP == 32 ? 1 : 0) : 1;
-  static constexpr bool MERGE_K = KBLK > 1;
-  static constexpr bool DKB_MERGED = (D == 32 && RP == 32);  // dKb columns sit behind the dK columns
+  //   dK chain:  dS^T . [Q | Qb]   (when Qb is 32 columns wide)        dQ chain:  dS . [K | Kc]
+  static constexpr bool MERGE_K = (D == 32 && RP == 32);
   static constexpr bool MERGE_Q = (D == 32 && RC == 32);
+  // resident tiles of the key block: K, (hi, lo) of k*scale when the scale is not a power of two, Kb, Kc, V
   static constexpr int OFF_K = 0;
-  static constexpr int OFF_KB = OFF_K + D_BYTES;
+  static constexpr int OFF_KS = OFF_K + D_BYTES;
+  static constexpr int OFF_KB = OFF_KS + (NQ == 2 ? 2 * D_BYTES : 0);
   static constexpr int OFF_KC = OFF_KB + R_BYTES;  // centred k_bias tile (dq_bias only)
   static constexpr int OFF_V = OFF_KC + RC_BYTES;
-  static constexpr int OFF_STAGE = OFF_V + D_BYTES;
-  static constexpr int OFF_PDS = OFF_STAGE + 2 * STAGE_BYTES;
+  static constexpr int KV_BYTES = OFF_V + D_BYTES;
+  static constexpr int OFF_STAGE = KV_BYTES;
   static constexpr int TAIL_BYTES = 256 + 8192 + 4 * RCX * 4 + 1024;  // barriers, row sums, centre keys, alignment
-  // P and dS tiles are double-buffered when shared memory allows it, so that the exponentials of
-  // query tile i+1 overlap the dV/dK/dQ MMAs of query tile i.
-  static constexpr bool PIPE = (D == 32) && (OFF_PDS + 2 * PDS_BYTES + TAIL_BYTES <= 227 * 1024);
-  static constexpr int NBUF = PIPE ? 2 : 1;
-  static constexpr int OFF_BAR = OFF_PDS + NBUF * PDS_BYTES;
+  // One P and one dS buffer: the compute warps keep the 16-bit P and dS of a query tile in registers until the
+  // tile's arithmetic is done and only then wait for the products of the previous tile to release the buffers.
+  // STAGED: a staging tile from which the fp32 dQ tile is reduced into global memory in bulk.
+  static constexpr int BASE_BYTES = KV_BYTES + 2 * TILE128 + TAIL_BYTES;
+  // (and a [128][rank] tile for dq_bias, rank <= RC / 2)
+  static constexpr int STG_WANT = 128 * D * 4 + 256 * RC;
+  static constexpr bool STAGED = BASE_BYTES + 2 * STAGE_BYTES + STG_WANT <= 227 * 1024;
+  static constexpr int STG_BYTES = STAGED ? STG_WANT : 0;
+  static constexpr int FIXED_BYTES = BASE_BYTES + STG_BYTES;
+  // as many stages of the query-tile ring as fit (2 or 3): a load takes longer than the products that free a stage
+  static constexpr int NSTAGE = (FIXED_BYTES + 3 * STAGE_BYTES <= 227 * 1024) ? 3 : 2;
+  static constexpr int OFF_P = OFF_STAGE + NSTAGE * STAGE_BYTES;
+  static constexpr int OFF_DS = OFF_P + TILE128;
+  static constexpr int OFF_STG = OFF_DS + TILE128;
+  static constexpr int OFF_BAR = OFF_STG + STG_BYTES;
   static constexpr int OFF_ROWSUM = OFF_BAR + 256;   // 4 x 4 x 128 floats: dS row sums per 32-key group
   static constexpr int OFF_KBC = OFF_ROWSUM + 8192;  // 4 x RCX floats: k_bias of the 4 centre keys
-  static constexpr int SMEM = OFF_PDS + NBUF * PDS_BYTES + TAIL_BYTES;
+  static constexpr int SMEM = FIXED_BYTES + NSTAGE * STAGE_BYTES;
   // tensor-memory columns
-  static constexpr int DK_COLS = MERGE_K ? 32 * KBLK : D;  // a split query adds its lo product in place otherwise
+  static constexpr int DK_COLS = MERGE_K ? 64 : D;  // dKb sits behind dK when the operands are merged
   static constexpr int T_S = 0, T_DP = 128, T_DV = 256, T_DK = T_DV + D;
-  static constexpr int T_DKB = DKB_MERGED ? T_DK + 32 * NQ : T_DK + DK_COLS;
-  static constexpr int T_DQ = T_DK + DK_COLS + (DKB_MERGED ? 0 : RP);
+  static constexpr int T_DKB = MERGE_K ? T_DK + 32 : T_DK + DK_COLS;
+  static constexpr int T_DQ = T_DK + DK_COLS + (MERGE_K ? 0 : RP);
   static constexpr int T_DQB = T_DQ + D, T_END = T_DQB + RC;
   // a second dQ|dQb accumulator when tensor memory has room: the dQ MMAs of query tile i+1 then do not wait
   // for the drain of tile i
@@ -150,7 +159,8 @@ __global__ void __launch_bounds__(512, 1)
 bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                  const __grid_constant__ CUtensorMap tmQb, const __grid_constant__ CUtensorMap tmKb,
-                 const __grid_constant__ CUtensorMap tmKc, const BwdArgs a) {
+                 const __grid_constant__ CUtensorMap tmKc, const __grid_constant__ CUtensorMap tmKs,
+                 const BwdArgs a) {
   using Cfg = BwdCfg<D, RP, NQ>;
   constexpr int RPX = Cfg::RPX;
   constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
@@ -159,12 +169,15 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
-  const uint32_t sK = sbase + Cfg::OFF_K, sKb = sbase + Cfg::OFF_KB, sKc = sbase + Cfg::OFF_KC, sV = sbase + Cfg::OFF_V,
-                 sStage = sbase + Cfg::OFF_STAGE, sPDS = sbase + Cfg::OFF_PDS;
+  const uint32_t sK = sbase + Cfg::OFF_K, sKs = sbase + Cfg::OFF_KS, sKb = sbase + Cfg::OFF_KB,
+                 sKc = sbase + Cfg::OFF_KC, sV = sbase + Cfg::OFF_V, sStage = sbase + Cfg::OFF_STAGE,
+                 sP = sbase + Cfg::OFF_P, sDS = sbase + Cfg::OFF_DS, sStg = sbase + Cfg::OFF_STG,
+                 sStgB = sStg + 128 * D * 4;
   const uint32_t bar0 = sbase + Cfg::OFF_BAR;
-  const uint32_t kv_full = bar0, s_full = bar0 + 8, dp_full = bar0 + 16, pds_ready = bar0 + 136 /*2*/,
-                 dq_full = bar0 + 32 /*2*/, dq_drained = bar0 + 152 /*2*/, sdp_read = bar0 + 24, qdo_full = bar0 + 48 /*2*/, qdo_free = bar0 + 64 /*2*/,
-                 pds_free = bar0 + 80 /*2*/, all_done = bar0 + 112, stg_free = bar0 + 120 /*2*/;
+  const uint32_t kv_full = bar0, s_full = bar0 + 8, dp_full = bar0 + 16, sdp_read = bar0 + 24,
+                 dq_full = bar0 + 32 /*2*/, qdo_full = bar0 + 48 /*3*/, qdo_free = bar0 + 72 /*3*/,
+                 all_done = bar0 + 112, pds_free = bar0 + 120, pds_ready = bar0 + 136 /*2*/,
+                 dq_drained = bar0 + 152 /*2*/;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::OFF_BAR + 96);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::OFF_BAR + 104);
 
@@ -191,15 +204,16 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(dp_full, 1);
       mbar_init(sdp_read, 8);  // every compute warp has S and dP of the tile in registers
       mbar_init(all_done, 4);  // one commit per issuing thread
-      for (int i = 0; i < 2; ++i) {
+      mbar_init(pds_free, 3);  // the dV(+dKb), dK and dQ chains have read P and dS of a query tile
+      for (int i = 0; i < 3; ++i) {
         mbar_init(qdo_full + 8 * i, 1);
         mbar_init(qdo_free + 8 * i, 3);  // S|dP, dV and dK chains read a stage
-        mbar_init(pds_free + 8 * i, 3);  // dV, dK and dQ chains read a P/dS buffer
+      }
+      for (int i = 0; i < 2; ++i) {
         mbar_init(dq_full + 8 * i, 1);
         mbar_init(dq_drained + 8 * i, 4);  // the drain warps
         mbar_init(pds_ready + 8 * i, 8);   // the compute warps; alternating by query tile, as the issuers wait at
                                            // different times
-        mbar_init(stg_free + 8 * i, 1);  // the drain thread that issued the bulk reduction
       }
       mbar_fence_init();
     }
@@ -218,40 +232,40 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (warp >= 12) {
   setmaxnreg_dec<80>();
   if (warp == 12) {
-    // ------------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------------ TMA producer, dQ | dQb chain
     if (lane == 0 && n_it > 0) {
       const int hq = a.hq_bcast ? 0 : h, bq = a.bq_bcast ? 0 : b;
       const int hk = a.hk_bcast ? 0 : h, bk = a.bk_bcast ? 0 : b;
-      mbar_expect_tx(kv_full, 2 * Cfg::D_BYTES + Cfg::R_BYTES + Cfg::RC_BYTES);
+      mbar_expect_tx(kv_full, Cfg::KV_BYTES);
       tma_tile_bwd<D>(sK, &tmK, kv_full, k0, h, b);
+      if (NQ == 2) {
+        tma_tile_bwd<D>(sKs, &tmKs, kv_full, k0, h, b);
+        tma_tile_bwd<D>(sKs + Cfg::D_BYTES, &tmKs, kv_full, k0, h, b, D);
+      }
       if (RP) tma_tile_bwd<RPX>(sKb, &tmKb, kv_full, k0, hk, bk);
       if (RP) tma_tile_bwd<Cfg::RCX>(sKc, &tmKc, kv_full, k0, hk, bk);
       tma_tile_bwd<D>(sV, &tmV, kv_full, k0, h, b);
       auto load_tile = [&](int it) {
-        const int st = it & 1;
+        const int st = it % Cfg::NSTAGE;
         const uint32_t base = sStage + st * Cfg::STAGE_BYTES;
         mbar_expect_tx(qdo_full + 8 * st, Cfg::STAGE_BYTES);
         const int q0 = (i_begin + it) * 128;
         tma_tile_bwd<D>(base, &tmQ, qdo_full + 8 * st, q0, h, b);
-        if (NQ == 2) tma_tile_bwd<D>(base + Cfg::OFF_QLO, &tmQ, qdo_full + 8 * st, q0, h, b, D);
         if (RP) tma_tile_bwd<RPX>(base + Cfg::OFF_QB, &tmQb, qdo_full + 8 * st, q0, hq, bq);
         tma_tile_bwd<D>(base + Cfg::OFF_DO, &tmDO, qdo_full + 8 * st, q0, h, b);
       };
-      load_tile(0);
-      if (n_it > 1) load_tile(1);
+      for (int it = 0; it < Cfg::NSTAGE && it < n_it; ++it) load_tile(it);
       // The same thread issues the dQ | dQb products: they become due when a query tile's P/dS are written,
       // the next load when the other chains have finished with that tile's stage -- in this order, every tile.
       constexpr uint32_t idQD = instr_desc(kBf16, false, true, 128, D);             // dQ: A K-major, B MN-major
       constexpr uint32_t idQM = instr_desc(kBf16, false, true, 128, D + Cfg::RCX);  // dQ|dQb merged
       constexpr uint32_t idQC = instr_desc(kBf16, false, true, 128, Cfg::RCX);      // dQb alone
-      const DescBase kDS = kmajor_base<128>(sPDS + tile_bytes(128)), mK = mnmajor_base<D>(sK),
-                     mKc = mnmajor_base<Cfg::RCX>(sKc);
-      const uint64_t dKKc = smem_desc(sK, Cfg::OFF_KC - Cfg::OFF_K, 8 * 64, 64);  // [K | Kc], 32-column blocks
+      const DescBase kDS = kmajor_base<128>(sDS), mK = mnmajor_base<D>(sK), mKc = mnmajor_base<Cfg::RCX>(sKc);
+      // [K | Kc]: 32-column blocks of 64-byte-swizzled rows, the second block at the distance between the tiles
+      const uint64_t dKKc = smem_desc(sK, Cfg::OFF_KC - Cfg::OFF_K, 8 * 64, 64);
       const DescBase mKKc{(uint32_t)dKKc, (uint32_t)(dKKc >> 32)};
       mbar_wait(kv_full, 0, abort_flag, a.status);
       auto issue_dQ = [&](int it) {
-        const int buf = Cfg::PIPE ? (it & 1) : 0;
-        const uint32_t po = buf * Cfg::PDS_BYTES;
         const int qb = it % Cfg::NDQ;  // dQ|dQb accumulator of this tile
         const uint32_t tq = tmem + qb * Cfg::DQ_STRIDE;
         mbar_wait(pds_ready + 8 * (it & 1), (it >> 1) & 1, abort_flag, a.status);
@@ -263,27 +277,27 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
           for (int s = 0; s < 8; ++s) {  // contraction over the 128 keys
             if (Cfg::MERGE_Q) {
-              umma_ss(tq + Cfg::T_DQ, desc_at(kDS, po + kmajor_step<128>(s)), desc_at(mKKc, mnmajor_step<D>(s)),
+              umma_ss(tq + Cfg::T_DQ, desc_at(kDS, kmajor_step<128>(s)), desc_at(mKKc, mnmajor_step<D>(s)),
                       idQM, s > 0);
             } else {
-              umma_ss(tq + Cfg::T_DQ, desc_at(kDS, po + kmajor_step<128>(s)), desc_at(mK, mnmajor_step<D>(s)),
+              umma_ss(tq + Cfg::T_DQ, desc_at(kDS, kmajor_step<128>(s)), desc_at(mK, mnmajor_step<D>(s)),
                       idQD, s > 0);
               if (RP)
-                umma_ss(tq + Cfg::T_DQB, desc_at(kDS, po + kmajor_step<128>(s)),
+                umma_ss(tq + Cfg::T_DQB, desc_at(kDS, kmajor_step<128>(s)),
                         desc_at(mKc, mnmajor_step<Cfg::RCX>(s)), idQC, s > 0);
             }
           }
         }
         umma_commit(dq_full + 8 * qb);
-        umma_commit(pds_free + 8 * buf);  // this chain no longer reads the P/dS buffer of the tile
+        umma_commit(pds_free);  // this chain no longer reads dS of the tile
         FB_TRACE_MARK(it, 11);
       };
 #pragma unroll 1
       for (int it = 0; it < n_it; ++it) {
         issue_dQ(it);
-        if (it + 2 < n_it) {  // the S|dP, dV and dK chains have finished reading the stage of tile it
-          mbar_wait(qdo_free + 8 * (it & 1), (it >> 1) & 1, abort_flag, a.status);
-          load_tile(it + 2);
+        if (it + Cfg::NSTAGE < n_it) {  // the S|dP, dV and dK chains have finished reading the stage of tile it
+          mbar_wait(qdo_free + 8 * (it % Cfg::NSTAGE), (it / Cfg::NSTAGE) & 1, abort_flag, a.status);
+          load_tile(it + Cfg::NSTAGE);
         }
       }
       umma_commit(all_done);
@@ -296,35 +310,30 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // run concurrently:
     //   warp 13  S and dP of query tile i, as soon as tile i-1 is in registers
     //   warp 14  dV (and dKb when it is a separate accumulator)
-    //   warp 15  dK (or dK(hi) | dK(lo) | dKb merged)
+    //   warp 15  dK (or dK | dKb merged)
     // Every accumulator is only ever touched by one thread, which keeps its MMAs ordered.
     if (lane == 0 && n_it > 0) {
       const int role = warp - 13;
       constexpr uint32_t idS = instr_desc(kBf16, false, false, 128, 128);  // S, dP: both operands K-major
       constexpr uint32_t idTD = instr_desc(kBf16, true, true, 128, D);     // dV, dK: A^T (MN-major), B MN-major
       constexpr uint32_t idTR = instr_desc(kBf16, true, true, 128, RPX);   // dKb
-      constexpr uint32_t idKM = instr_desc(kBf16, true, true, 128, Cfg::MERGE_K ? 32 * Cfg::KBLK : 32);  // merged dK
-      // descriptor views built once (stage 0 / buffer 0); each MMA adds a constant to the address field
-      const DescBase mP = mnmajor_base<128>(sPDS), mDS = mnmajor_base<128>(sPDS + tile_bytes(128));
-      // merged views (head_dim 32): 32-column blocks of 64-byte-swizzled rows, the next block found at a
-      // leading-dimension offset of the distance between the tiles
-      const uint64_t dQall = smem_desc(sStage, Cfg::D_BYTES, 8 * 64, 64);
-      const DescBase mQall{(uint32_t)dQall, (uint32_t)(dQall >> 32)};
+      constexpr uint32_t idKM = instr_desc(kBf16, true, true, 128, 64);    // dK | dKb merged
       mbar_wait(kv_full, 0, abort_flag, a.status);
       tc_fence_after_sync();
       if (role == 0) {
+        // descriptor views built once (stage 0); each MMA adds a constant to the address field
         const DescBase kQ = kmajor_base<D>(sStage), kDO = kmajor_base<D>(sStage + Cfg::OFF_DO),
-                       kQb = kmajor_base<RPX>(sStage + Cfg::OFF_QB), kK = kmajor_base<D>(sK),
+                       kQb = kmajor_base<RPX>(sStage + Cfg::OFF_QB), kK = kmajor_base<D>(NQ == 2 ? sKs : sK),
                        kKb = kmajor_base<RPX>(sKb), kV = kmajor_base<D>(sV);
 #pragma unroll 1
         for (int it = 0; it < n_it; ++it) {
-          const int st = it & 1;
+          const int st = it % Cfg::NSTAGE;
           const uint32_t so = st * Cfg::STAGE_BYTES;
           if (it > 0) {  // the compute warps hold S and dP of the previous tile in registers
             mbar_wait(sdp_read, (it - 1) & 1, abort_flag, a.status);
             tc_fence_after_sync();
           }
-          mbar_wait(qdo_full + 8 * st, (it >> 1) & 1, abort_flag, a.status);
+          mbar_wait(qdo_full + 8 * st, (it / Cfg::NSTAGE) & 1, abort_flag, a.status);
           tc_fence_after_sync();
           FB_TRACE_MARK(it, 4);
           // bias products first, into the empty accumulator (large factor terms cancel among themselves)
@@ -335,11 +344,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                       s > 0);
           }
 #pragma unroll
-          for (int t = 0; t < NQ; ++t) {  // query terms share the K tile
+          for (int t = 0; t < NQ; ++t) {  // key terms (k, or hi and lo of k*scale) share the Q tile
 #pragma unroll
             for (int s = 0; s < D / 16; ++s)
-              umma_ss(tmem + Cfg::T_S, desc_at(kQ, so + (t ? Cfg::OFF_QLO : 0) + kmajor_step<D>(s)),
-                      desc_at(kK, kmajor_step<D>(s)), idS, (RP || t > 0 || s > 0) ? 1u : 0u);
+              umma_ss(tmem + Cfg::T_S, desc_at(kQ, so + kmajor_step<D>(s)),
+                      desc_at(kK, t * Cfg::D_BYTES + kmajor_step<D>(s)), idS, (RP || t > 0 || s > 0) ? 1u : 0u);
           }
           umma_commit(s_full);
 #pragma unroll
@@ -352,15 +361,17 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       } else {
         const DescBase mQ = mnmajor_base<D>(sStage), mDO = mnmajor_base<D>(sStage + Cfg::OFF_DO),
-                       mQb = mnmajor_base<RPX>(sStage + Cfg::OFF_QB);
+                       mQb = mnmajor_base<RPX>(sStage + Cfg::OFF_QB), mP = mnmajor_base<128>(sP),
+                       mDS = mnmajor_base<128>(sDS);
+        // [Q | Qb]: 32-column blocks of 64-byte-swizzled rows, the second block at the distance between the tiles
+        const uint64_t dQQb = smem_desc(sStage, Cfg::OFF_QB, 8 * 64, 64);
+        const DescBase mQQb{(uint32_t)dQQb, (uint32_t)(dQQb >> 32)};
 #pragma unroll 1
         for (int it = 0; it < n_it; ++it) {
-          const int st = it & 1;
+          const int st = it % Cfg::NSTAGE;
           const uint32_t so = st * Cfg::STAGE_BYTES;
-          const int buf = Cfg::PIPE ? st : 0;
-          const uint32_t po = buf * Cfg::PDS_BYTES;
           const uint32_t acc0 = it > 0 ? 1u : 0u;
-          mbar_wait(qdo_full + 8 * st, (it >> 1) & 1, abort_flag, a.status);
+          mbar_wait(qdo_full + 8 * st, (it / Cfg::NSTAGE) & 1, abort_flag, a.status);
           mbar_wait(pds_ready + 8 * (it & 1), (it >> 1) & 1, abort_flag, a.status);
           tc_fence_after_sync();
           FB_TRACE_MARK(it, 4 + 2 * role);
@@ -368,33 +379,27 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           } else if (role == 1) {
 #pragma unroll
             for (int s = 0; s < 8; ++s)  // contraction over the 128 query rows
-              umma_ss(tmem + Cfg::T_DV, desc_at(mP, po + mnmajor_step<128>(s)), desc_at(mDO, so + mnmajor_step<D>(s)),
-                      idTD, (acc0 | (s > 0)) ? 1u : 0u);
-            if (RP && !Cfg::DKB_MERGED) {
+              umma_ss(tmem + Cfg::T_DV, desc_at(mP, mnmajor_step<128>(s)), desc_at(mDO, so + mnmajor_step<D>(s)), idTD,
+                      (acc0 | (s > 0)) ? 1u : 0u);
+            if (RP && !Cfg::MERGE_K) {
 #pragma unroll
               for (int s = 0; s < 8; ++s)
-                umma_ss(tmem + Cfg::T_DKB, desc_at(mDS, po + mnmajor_step<128>(s)),
+                umma_ss(tmem + Cfg::T_DKB, desc_at(mDS, mnmajor_step<128>(s)),
                         desc_at(mQb, so + mnmajor_step<RPX>(s)), idTR, (acc0 | (s > 0)) ? 1u : 0u);
             }
-          } else if (Cfg::MERGE_K) {  // dK(hi) | dK(lo) | dKb in one accumulator
-#pragma unroll
-            for (int s = 0; s < 8; ++s)
-              umma_ss(tmem + Cfg::T_DK, desc_at(mDS, po + mnmajor_step<128>(s)),
-                      desc_at(mQall, so + mnmajor_step<D>(s)), idKM, (acc0 | (s > 0)) ? 1u : 0u);
           } else {
 #pragma unroll
-            for (int s = 0; s < 8; ++s)
-              umma_ss(tmem + Cfg::T_DK, desc_at(mDS, po + mnmajor_step<128>(s)),
-                      desc_at(mQ, so + mnmajor_step<D>(s)), idTD, (acc0 | (s > 0)) ? 1u : 0u);
-            if (NQ == 2) {  // dK += dS^T . lo(q*scale)
-#pragma unroll
-              for (int s = 0; s < 8; ++s)
-                umma_ss(tmem + Cfg::T_DK, desc_at(mDS, po + mnmajor_step<128>(s)),
-                        desc_at(mQ, so + Cfg::OFF_QLO + mnmajor_step<D>(s)), idTD, 1);
+            for (int s = 0; s < 8; ++s) {
+              if (Cfg::MERGE_K)
+                umma_ss(tmem + Cfg::T_DK, desc_at(mDS, mnmajor_step<128>(s)),
+                        desc_at(mQQb, so + mnmajor_step<D>(s)), idKM, (acc0 | (s > 0)) ? 1u : 0u);
+              else
+                umma_ss(tmem + Cfg::T_DK, desc_at(mDS, mnmajor_step<128>(s)),
+                        desc_at(mQ, so + mnmajor_step<D>(s)), idTD, (acc0 | (s > 0)) ? 1u : 0u);
             }
           }
           umma_commit(qdo_free + 8 * st);
-          umma_commit(pds_free + 8 * buf);  // this chain no longer reads the P/dS buffer of the tile
+          umma_commit(pds_free);  // this chain no longer reads P / dS of the tile
           FB_TRACE_MARK(it, 5 + 2 * role);
         }
       }
@@ -418,17 +423,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         mbar_wait(dq_full + 8 * qb, (it / Cfg::NDQ) & 1, abort_flag, a.status);
         tc_fence_after_sync();
         if (warp == 8 && lane == 0) FB_TRACE_MARK(it, 12);
-        if (FB_DBG(2)) {
-          if (Cfg::PIPE) {
-            mbar_wait(pds_free + 8 * (it & 1), (it >> 1) & 1, abort_flag, a.status);
-            mbar_arrive_warp(stg_free + 8 * (it & 1));
-          }
-          tc_fence_before_sync();
-          mbar_arrive_warp(dq_drained + 8 * qb);
-          continue;
-        }
-        if (!Cfg::PIPE) {
-          // single P/dS buffer: no spare tile to stage in, reduce straight from registers (one row per thread)
+        if (!Cfg::STAGED) {
+          // no staging tile: reduce straight from registers (one row per thread)
           float* dst = a.dq_acc + (((int64_t)b * a.Sq + grow) * a.H + h) * D;
 #pragma unroll 1
           for (int c0 = 0; c0 < D; c0 += 32) {
@@ -445,31 +441,23 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         } else {
           // dQ tile: TMEM -> registers -> shared-memory staging -> ONE bulk reduction into the fp32 accumulator.
           // Per-thread vector reductions (32 per row) crowd the load/store unit that the compute warps need for
-          // their P/dS stores and row statistics; the bulk form is executed by the copy engine.  The staging area
-          // is the P tile of the buffer the MMAs of this query tile have finished reading; it is handed back
-          // through stg_free.
-          const int buf = Cfg::PIPE ? (it & 1) : 0;
-          const uint32_t stage = sPDS + buf * Cfg::PDS_BYTES;
-          // dq_full only covers the dQ chain: the dV chain (another thread) must be done with the P tile as well
-          mbar_wait(pds_free + 8 * buf, (it >> 1) & 1, abort_flag, a.status);
-#pragma unroll 1
-          for (int c0 = 0; c0 < D; c0 += 16) {
-            uint32_t r[16];
-            tmem_ld16(tq + Cfg::T_DQ + c0, r);
-            tmem_wait_ld(r);
-#pragma unroll
-            for (int g = 0; g < 4; ++g)
-              st_shared_v4(stage + dq_stage_off(row, c0 / 4 + g), r[g * 4], r[g * 4 + 1], r[g * 4 + 2], r[g * 4 + 3]);
-          }
-          fence_proxy_async_smem();  // the staged tile becomes visible to the copy engine
+          // their P/dS stores; the bulk form is executed by the copy engine.
+          // the thread that issued the previous tile's reduction has seen its shared-memory reads complete
           asm volatile("bar.sync 3, 128;" ::: "memory");  // the drain warpgroup only
-          if (warp == 8 && lane == 0) {
-            if (!FB_DBG(1))
-              bulk_reduce_add_f32(a.dq_acc + ((int64_t)bh * a.nq_tiles + (i_begin + it)) * (128 * D), stage,
-                                  128 * D * 4);
-            bulk_commit_group();
-            bulk_wait_group_read0();
-            mbar_arrive(stg_free + 8 * buf);  // staging reads done: the P tile may be rewritten
+#pragma unroll 1
+          for (int c0 = 0; c0 < D; c0 += 32) {
+            uint32_t r0[16], r1[16];
+            tmem_ld16(tq + Cfg::T_DQ + c0, r0);
+            tmem_ld16(tq + Cfg::T_DQ + c0 + 16, r1);
+            tmem_wait_ld(r0);
+            tmem_wait_ld(r1);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              st_shared_v4(sStg + dq_stage_off(row, c0 / 4 + g), r0[g * 4], r0[g * 4 + 1], r0[g * 4 + 2],
+                           r0[g * 4 + 3]);
+              st_shared_v4(sStg + dq_stage_off(row, c0 / 4 + 4 + g), r1[g * 4], r1[g * 4 + 1], r1[g * 4 + 2],
+                           r1[g * 4 + 3]);
+            }
           }
         }
         if (RP) {
@@ -481,34 +469,53 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
           for (int g = 0; g < 4; ++g) rsum[g] = s_rowsum[g * 128 + row];
           const int bq = a.bq_bcast ? 0 : b, hq = a.hq_bcast ? 0 : h;
-          float* dstb = a.dqb_acc + (((int64_t)bq * a.Sq + grow) * a.Hq + hq) * a.R;
+          // accumulator laid out (Bq, Hq, query rows padded to whole tiles, R): a tile's rows are contiguous
+          float* tileb = a.dqb_acc + (((int64_t)bq * a.Hq + hq) * a.nq_tiles + (i_begin + it)) * (128 * a.R);
+          float* stgb = reinterpret_cast<float*>(smem + Cfg::OFF_STG + 128 * D * 4) + row * a.R;
           const int used = 2 * a.R;  // (hi, lo) column groups of the centred factor
 #pragma unroll 1
           for (int c0 = 0; c0 < Cfg::RCX && c0 < used; c0 += 16) {
             uint32_t r[16];
             tmem_ld16(tq + Cfg::T_DQB + c0, r);
             tmem_wait_ld(r);
-            if (grow < a.Sq && !FB_DBG(1)) {
 #pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                const int c = c0 + i;
-                if (c < a.R) {
-                  float v = __uint_as_float(r[i]);
+            for (int i = 0; i < 16; ++i) {
+              const int c = c0 + i;
+              if (c < a.R) {
+                float v = __uint_as_float(r[i]);
 #pragma unroll
-                  for (int g = 0; g < 4; ++g) v = fmaf(s_kbc[g * Cfg::RCX + c], rsum[g], v);
-                  atomicAdd(dstb + c, v);
-                } else if (c < used) {
-                  atomicAdd(dstb + c - a.R, __uint_as_float(r[i]));
-                }
+                for (int g = 0; g < 4; ++g) v = fmaf(s_kbc[g * Cfg::RCX + c], rsum[g], v);
+                if (Cfg::STAGED) stgb[c] = v;
+                else if (grow < a.Sq) atomicAdd(tileb + row * a.R + c, v);
+              } else if (c < used) {
+                if (Cfg::STAGED) stgb[c - a.R] += __uint_as_float(r[i]);
+                else if (grow < a.Sq) atomicAdd(tileb + row * a.R + c - a.R, __uint_as_float(r[i]));
               }
             }
           }
         }
         tc_fence_before_sync();
         if (warp == 8 && lane == 0) FB_TRACE_MARK(it, 13);
-        mbar_arrive_warp(dq_drained + 8 * qb);
+        mbar_arrive_warp(dq_drained + 8 * qb);  // every tensor-memory read of the tile is done
+        if (Cfg::STAGED) {
+          fence_proxy_async_smem();  // the staged tiles become visible to the copy engine
+          asm volatile("bar.sync 3, 128;" ::: "memory");
+          if (warp == 8 && lane == 0) {
+            if (!FB_DBG(1))
+              bulk_reduce_add_f32(a.dq_acc + ((int64_t)bh * a.nq_tiles + (i_begin + it)) * (128 * D), sStg,
+                                  128 * D * 4);
+            if (RP && !FB_DBG(16)) {
+              const int bq = a.bq_bcast ? 0 : b, hq = a.hq_bcast ? 0 : h;
+              bulk_reduce_add_f32(
+                  a.dqb_acc + (((int64_t)bq * a.Hq + hq) * a.nq_tiles + (i_begin + it)) * (128 * a.R), sStgB,
+                  128 * a.R * 4);
+            }
+            bulk_commit_group();
+            bulk_wait_group_read0();
+          }
+        }
       }
-      if (Cfg::PIPE && warp == 8 && lane == 0) bulk_wait_group0();  // reductions complete before the CTA exits
+      if (Cfg::STAGED && warp == 8 && lane == 0) bulk_wait_group0();  // reductions complete before the CTA exits
     }
   } else if (n_it > 0) {
     // ------------------------------------------------------------------ compute warpgroups (warps 0-7)
@@ -550,7 +557,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int grow = q0 + row;
       // a row that saw no key has lse = -inf: make its probabilities exactly zero
       const float lse2_cur = lse_raw == -INFINITY ? INFINITY : lse_raw * kLog2e, dlt_cur = dlt;
-      const uint32_t sP_cur = sPDS + (Cfg::PIPE ? (it & 1) : 0) * Cfg::PDS_BYTES;  // P tile, dS tile behind it
       const bool need_mask = (a.causal && k0 + 127 > q0) || (k0 + 128 > a.Sk);
       float ds_sum0 = 0.f, ds_sum1 = 0.f;  // fp32 row sums of dS over this thread's two 32-column groups
       if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 14);
@@ -573,17 +579,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc_fence_before_sync();
       mbar_arrive_warp(sdp_read);
       if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 2);
-      // the MMAs that read this P/dS buffer last (query tile it - NBUF) have completed
-      if (it >= Cfg::NBUF) {
-        if (Cfg::PIPE) {
-          mbar_wait(pds_free + 8 * (it & 1), ((it >> 1) - 1) & 1, abort_flag, a.status);
-          mbar_wait(stg_free + 8 * (it & 1), ((it >> 1) - 1) & 1, abort_flag, a.status);
-        } else {
-          mbar_wait(pds_free, (it - 1) & 1, abort_flag, a.status);
-        }
-      }
       if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 3);
-      auto chunk = [&](uint32_t (&rs)[32], uint32_t (&rd)[32], int c) {
+      // P and dS of the tile stay in registers as packed 16-bit pairs (16 words per 32-column chunk each) until
+      // both chunks are done: the shared-memory tiles are still being read by the products of the previous tile
+      auto chunk = [&](uint32_t (&rs)[32], uint32_t (&rd)[32], uint32_t (&pk)[16], uint32_t (&dk)[16], int c) {
         const int col0 = wg * 64 + c * 32;
         float sum0 = 0.f, sum1 = 0.f;
         // the masked and the unmasked tile get separate straight-line loops: a per-element test of need_mask
@@ -604,27 +603,29 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         };
         if (need_mask) elems(std::true_type{}); else elems(std::false_type{});
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint4 wp, wd;
-          wp.x = Pack2<T>::pack(__uint_as_float(rs[g * 8 + 0]), __uint_as_float(rs[g * 8 + 1]));
-          wp.y = Pack2<T>::pack(__uint_as_float(rs[g * 8 + 2]), __uint_as_float(rs[g * 8 + 3]));
-          wp.z = Pack2<T>::pack(__uint_as_float(rs[g * 8 + 4]), __uint_as_float(rs[g * 8 + 5]));
-          wp.w = Pack2<T>::pack(__uint_as_float(rs[g * 8 + 6]), __uint_as_float(rs[g * 8 + 7]));
-          wd.x = Pack2<T>::pack(__uint_as_float(rd[g * 8 + 0]), __uint_as_float(rd[g * 8 + 1]));
-          wd.y = Pack2<T>::pack(__uint_as_float(rd[g * 8 + 2]), __uint_as_float(rd[g * 8 + 3]));
-          wd.z = Pack2<T>::pack(__uint_as_float(rd[g * 8 + 4]), __uint_as_float(rd[g * 8 + 5]));
-          wd.w = Pack2<T>::pack(__uint_as_float(rd[g * 8 + 6]), __uint_as_float(rd[g * 8 + 7]));
-          const uint32_t off = tile_chunk_offset<128>(row, col0 + g * 8);
-          st_shared_v4(sP_cur + off, wp.x, wp.y, wp.z, wp.w);
-          st_shared_v4(sP_cur + tile_bytes(128) + off, wd.x, wd.y, wd.z, wd.w);
+        for (int i = 0; i < 16; ++i) {
+          pk[i] = Pack2<T>::pack(__uint_as_float(rs[2 * i]), __uint_as_float(rs[2 * i + 1]));
+          dk[i] = Pack2<T>::pack(__uint_as_float(rd[2 * i]), __uint_as_float(rd[2 * i + 1]));
         }
         return sum0 + sum1;
       };
-      ds_sum0 = chunk(rs0, rd0, 0);
+      uint32_t pk0[16], pk1[16], dk0[16], dk1[16];
+      ds_sum0 = chunk(rs0, rd0, pk0, dk0, 0);
       if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 15);
       load_row_stats(it + 1, lse_raw, dlt);  // next tile's statistics: the loads complete under this tile's math
       if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 17);
-      ds_sum1 = chunk(rs1, rd1, 1);
+      ds_sum1 = chunk(rs1, rd1, pk1, dk1, 1);
+      if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 18);
+      // the dV, dK and dQ products of the previous query tile have read P and dS
+      if (it >= 1) mbar_wait(pds_free, (it - 1) & 1, abort_flag, a.status);
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const uint32_t o0 = tile_chunk_offset<128>(row, wg * 64 + g * 8), o1 = tile_chunk_offset<128>(row, wg * 64 + 32 + g * 8);
+        st_shared_v4(sP + o0, pk0[g * 4], pk0[g * 4 + 1], pk0[g * 4 + 2], pk0[g * 4 + 3]);
+        st_shared_v4(sDS + o0, dk0[g * 4], dk0[g * 4 + 1], dk0[g * 4 + 2], dk0[g * 4 + 3]);
+        st_shared_v4(sP + o1, pk1[g * 4], pk1[g * 4 + 1], pk1[g * 4 + 2], pk1[g * 4 + 3]);
+        st_shared_v4(sDS + o1, dk1[g * 4], dk1[g * 4 + 1], dk1[g * 4 + 2], dk1[g * 4 + 3]);
+      }
       if (RP) {
         // four buffers: the drain warpgroup may lag up to three query tiles behind
         float* s_rowsum = reinterpret_cast<float*>(smem + Cfg::OFF_ROWSUM) + (it & 3) * 512;
@@ -655,13 +656,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_ld16(tmem + Cfg::T_DK + lane_off + c0, rk);
         tmem_wait_ld(rv);
         tmem_wait_ld(rk);
-        if (Cfg::MERGE_K && NQ == 2) {  // the lo product of the split query sits 32 columns further
-          uint32_t rl[16];
-          tmem_ld16(tmem + Cfg::T_DK + 32 + lane_off + c0, rl);
-          tmem_wait_ld(rl);
-#pragma unroll
-          for (int i = 0; i < 16; ++i) rk[i] = __float_as_uint(__uint_as_float(rk[i]) + __uint_as_float(rl[i]));
-        }
         if (krow < a.Sk) {
 #pragma unroll
           for (int g = 0; g < 2; ++g) {
@@ -692,7 +686,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (krow < a.Sk) {
 #pragma unroll
           for (int i = 0; i < 16; ++i)
-            if (c0 + i < used) atomicAdd(dst + c0 + i, __uint_as_float(r[i]) * a.dk_scale);
+            if (c0 + i < used) atomicAdd(dst + c0 + i, __uint_as_float(r[i]) * a.dkb_scale);
         }
       }
     }
@@ -760,7 +754,8 @@ extern "C" int fb_debug_trace_bwd(long long* out, int n) {
 }
 namespace fb {
 #endif
-int store_factor_grads_from(const fb_params* p, float* dqb, float* dkb, cudaStream_t st);  // fb_general.cu
+int store_factor_grads_from(const fb_params* p, float* dqb, float* dkb, cudaStream_t st,
+                            int64_t dqb_head_major_rows = 0);  // fb_general.cu
 
 static bool rows_16b_ok(const void* ptr, const int64_t* st) {
   if (reinterpret_cast<uintptr_t>(ptr) & 15) return false;
@@ -781,7 +776,8 @@ static BwdWs bwd_layout(const fb_params* p, const PackPlan& plan) {
   w.off_dq = w.off_qs + plan.qs_bytes;
   // query rows padded to whole tiles: the bulk reductions of the backward write whole [128][D] tiles
   const size_t dq = round256((size_t)p->B * ((p->Sq + 127) / 128) * 128 * p->H * p->D * 4);
-  const size_t dqb = p->R ? round256((size_t)plan.Bq * p->Sq * plan.Hq * p->R * 4) : 0;
+  // (Bq, Hq, query rows padded to whole tiles, R): a query tile's rows are contiguous for the bulk reduction
+  const size_t dqb = p->R ? round256((size_t)plan.Bq * plan.Hq * ((p->Sq + 127) / 128) * 128 * p->R * 4) : 0;
   const size_t dkb = p->R ? round256((size_t)plan.Bk * p->Sk * plan.Hk * p->R * 4) : 0;
   w.off_dqb = w.off_dq + dq;
   w.off_dkb = w.off_dqb + dqb;
@@ -838,20 +834,20 @@ static int launch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t s
   }
   cudaError_t e = cudaMemsetAsync(ws + w.off_dq, 0, w.zero_bytes, st);
   if (e != cudaSuccess) return (int)e;
-  CUtensorMap tQ, tK, tV, tDO, tQb, tKb, tKc;
-  if (NQ == 2) {
-    // query operand = (hi, lo) of q*scale, laid out (B, H, Sq, 2D) in the workspace
-    void* qs = ws + w.off_qs;
-    if ((rc = launch_pack_qscaled(p, plan, qs, st))) return rc;
-    if ((rc = make_tmap_4d(&tQ, qs, 2 * D, p->Sq, p->H, p->B, 2 * D, (int64_t)2 * D * p->Sq,
-                           (int64_t)2 * D * p->Sq * p->H, D, 128)))
-      return rc;
-  } else if ((rc = make_tmap_4d(&tQ, p->q, D, p->Sq, p->H, p->B, p->q_stride[2], p->q_stride[1], p->q_stride[0], D,
-                                128))) {
+  CUtensorMap tQ, tK, tV, tDO, tQb, tKb, tKc, tKs;
+  if ((rc = make_tmap_4d(&tQ, p->q, D, p->Sq, p->H, p->B, p->q_stride[2], p->q_stride[1], p->q_stride[0], D, 128)))
     return rc;
+  if (NQ == 2) {
+    // key operand of S = (hi, lo) of k*scale, laid out (B, H, Sk, 2D) in the workspace
+    void* ks = ws + w.off_qs;
+    if ((rc = launch_pack_kscaled(p, plan, ks, st))) return rc;
+    if ((rc = make_tmap_4d(&tKs, ks, 2 * D, p->Sk, p->H, p->B, 2 * D, (int64_t)2 * D * p->Sk,
+                           (int64_t)2 * D * p->Sk * p->H, D, 128)))
+      return rc;
   }
   if ((rc = make_tmap_4d(&tK, p->k, D, p->Sk, p->H, p->B, p->k_stride[2], p->k_stride[1], p->k_stride[0], D, 128)))
     return rc;
+  if (NQ != 2) tKs = tK;
   if ((rc = make_tmap_4d(&tV, p->v, D, p->Sk, p->H, p->B, p->v_stride[2], p->v_stride[1], p->v_stride[0], D, 128)))
     return rc;
   if ((rc = make_tmap_4d(&tDO, p->dout, D, p->Sq, p->H, p->B, p->dout_stride[2], p->dout_stride[1],
@@ -881,8 +877,9 @@ static int launch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t s
   a.R = p->R;
   a.hq_bcast = plan.Hq == 1; a.bq_bcast = plan.Bq == 1; a.hk_bcast = plan.Hk == 1; a.bk_bcast = plan.Bk == 1;
   a.Hq = plan.Hq; a.Hk = plan.Hk;
-  // with a split query operand the scale is already inside S and inside the operands of dK / dk_bias
-  a.dk_scale = NQ == 2 ? 1.f : p->softmax_scale;
+  // with a split key operand the scale is already inside S
+  a.dk_scale = p->softmax_scale;                     // dK accumulates dS^T.q
+  a.dkb_scale = NQ == 2 ? 1.f : p->softmax_scale;    // the packed q-side factor carries 1/scale when nq == 1
   a.scale_log2 = (NQ == 2 ? 1.f : p->softmax_scale) * 1.4426950408889634f;
   a.lse = p->lse;
   a.delta = p->delta;
@@ -914,17 +911,17 @@ static int launch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t s
   }
   const unsigned grid = (unsigned)((int64_t)a.nk_tiles * p->B * p->H);
   prof_before(KC_BWD_MAIN, st);
-  kern<<<grid, 512, Cfg::SMEM, st>>>(tQ, tK, tV, tDO, tQb, tKb, tKc, a);
+  kern<<<grid, 512, Cfg::SMEM, st>>>(tQ, tK, tV, tDO, tQb, tKb, tKc, tKs, a);
   prof_after(KC_BWD_MAIN, st);
   note_launch();
   if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
   const int64_t n8 = ((int64_t)p->B * p->Sq * p->H * D) / 8;
   dq_store_kernel<T><<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(
       a.dq_acc, reinterpret_cast<T*>(p->dq), p->B, p->Sq, p->H, D, p->dq_stride[0], p->dq_stride[1], p->dq_stride[2],
-      p->softmax_scale, Cfg::PIPE ? 1 : 0);
+      p->softmax_scale, Cfg::STAGED ? 1 : 0);
   note_launch();
   if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
-  if (p->R > 0) return store_factor_grads_from(p, a.dqb_acc, a.dkb_acc, st);
+  if (p->R > 0) return store_factor_grads_from(p, a.dqb_acc, a.dkb_acc, st, (int64_t)a.nq_tiles * 128);
   return 0;
   }
 }

@@ -25,7 +25,8 @@ bool tma_compatible(const void* ptr, int64_t stride_row, int64_t stride_head, in
 //   nq == 1 (softmax_scale an exact power of two): the query operand is the caller's q, the q-side factor is
 //           q_bias / scale (exact), logits = scale * S.
 //   nq == 2: the query operand is q*scale as a (hi, lo) pair of 16-bit terms, laid out (B, H, Sq, 2D); factors
-//           are used as given, logits = S.
+//           are used as given, logits = S.  (The backward splits k*scale instead: its key tile is the resident
+//           one.)
 // Packed factors: (Bb, Hb, S, RP) contiguous, Bb/Hb = 1 on broadcast dims, zero-padded to RP columns.
 struct PackPlan {
   int nq;          // 1 or 2 query terms
@@ -41,6 +42,8 @@ bool plan_pack(const fb_params* p, PackPlan* plan, bool for_bwd = false);
 // kcenter (optional, rows of plan.RC columns): k_bias minus the k_bias of the middle key of each group of 32 keys.
 int launch_pack(const fb_params* p, const PackPlan& plan, void* qpack, void* kpack, void* kcenter, cudaStream_t st);
 int launch_pack_qscaled(const fb_params* p, const PackPlan& plan, void* qs, cudaStream_t st);
+// backward: (hi, lo) of k*scale, laid out (B, H, Sk, 2D)
+int launch_pack_kscaled(const fb_params* p, const PackPlan& plan, void* ks, cudaStream_t st);
 
 // ---- kernels ------------------------------------------------------------------------------------
 int launch_fwd_general(const fb_params* p, cudaStream_t st);

@@ -7,6 +7,8 @@
 //   * otherwise: qs = q * scale, stored as a (hi, lo) pair of 16-bit terms (contraction 2*head_dim),
 //     and qb = q_bias as given, so that the products of the bias factors stay exact and un-scaled --
 //     terms as large as an ALiBi position cancel inside one MMA instead of being rounded first.
+// The backward keeps its key tile resident and streams the query tiles, so it puts the split on the key side
+// instead: S = q.(k*scale), with k*scale as a (hi, lo) pair.
 // Factors are zero-padded to RP columns (16/32/64).  The backward also gets a centred k-side copy
 // (k_bias minus the k_bias of the middle key of its group of 32 keys, as a (hi, lo) pair).
 #include <math.h>
@@ -31,7 +33,8 @@ bool plan_pack(const fb_params* p, PackPlan* plan, bool for_bwd) {
   const bool pow2 = frexpf(p->softmax_scale, &e) == 0.5f;
   plan->nq = pow2 ? 1 : 2;
   plan->qb_mult = pow2 ? (float)(1.0 / (double)p->softmax_scale) : 1.f;
-  plan->qs_bytes = pow2 ? 0 : round256((size_t)p->B * p->H * p->Sq * 2 * p->D * 2);
+  // forward: scaled-query copy; backward: scaled-key copy
+  plan->qs_bytes = pow2 ? 0 : round256((size_t)p->B * p->H * (for_bwd ? p->Sk : p->Sq) * 2 * p->D * 2);
   plan->RC = 0;
   plan->kc_bytes = 0;
   if (p->R <= 0) {
@@ -92,7 +95,8 @@ __global__ void __launch_bounds__(256) pack_factor_kernel(const T* __restrict__ 
   }
 }
 
-// qs[b][h][s][0:D] = T(q * scale), qs[b][h][s][D:2D] = T(q * scale - hi): the scaled query as two 16-bit terms.
+// qs[b][h][s][0:D] = T(x * scale), qs[b][h][s][D:2D] = T(x * scale - hi): the scaled query (or key) as two 16-bit
+// terms.
 // One thread converts 8 consecutive elements (16-byte load, two 16-byte stores).
 template <typename T>
 __global__ void __launch_bounds__(256) pack_qscaled_kernel(const T* __restrict__ q, int64_t sb, int64_t sh, int64_t ss,
@@ -142,20 +146,30 @@ int launch_pack(const fb_params* p, const PackPlan& plan, void* qpack, void* kpa
                                   : launch_pack_t<__nv_bfloat16>(p, plan, qpack, kpack, kcenter, st);
 }
 
-int launch_pack_qscaled(const fb_params* p, const PackPlan& plan, void* qs, cudaStream_t st) {
-  if (plan.nq == 1) return 0;
-  const int64_t n = (int64_t)p->B * p->H * p->Sq * (p->D / 8);
+static int launch_pack_scaled(const fb_params* p, const void* src, const int64_t* stride, int S, void* dst,
+                              cudaStream_t st) {
+  const int64_t n = (int64_t)p->B * p->H * S * (p->D / 8);
   const unsigned blocks = (unsigned)((n + 255) / 256);
   if (p->dtype == FB_DTYPE_F16)
-    pack_qscaled_kernel<__half><<<blocks, 256, 0, st>>>(reinterpret_cast<const __half*>(p->q), p->q_stride[0],
-                                                        p->q_stride[1], p->q_stride[2], p->B, p->H, p->Sq, p->D,
-                                                        p->softmax_scale, reinterpret_cast<__half*>(qs));
+    pack_qscaled_kernel<__half><<<blocks, 256, 0, st>>>(reinterpret_cast<const __half*>(src), stride[0], stride[1],
+                                                        stride[2], p->B, p->H, S, p->D, p->softmax_scale,
+                                                        reinterpret_cast<__half*>(dst));
   else
     pack_qscaled_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(
-        reinterpret_cast<const __nv_bfloat16*>(p->q), p->q_stride[0], p->q_stride[1], p->q_stride[2], p->B, p->H,
-        p->Sq, p->D, p->softmax_scale, reinterpret_cast<__nv_bfloat16*>(qs));
+        reinterpret_cast<const __nv_bfloat16*>(src), stride[0], stride[1], stride[2], p->B, p->H, S, p->D,
+        p->softmax_scale, reinterpret_cast<__nv_bfloat16*>(dst));
   note_launch();
   return (int)cudaGetLastError();
+}
+
+int launch_pack_qscaled(const fb_params* p, const PackPlan& plan, void* qs, cudaStream_t st) {
+  if (plan.nq == 1) return 0;
+  return launch_pack_scaled(p, p->q, p->q_stride, p->Sq, qs, st);
+}
+
+int launch_pack_kscaled(const fb_params* p, const PackPlan& plan, void* ks, cudaStream_t st) {
+  if (plan.nq == 1) return 0;
+  return launch_pack_scaled(p, p->k, p->k_stride, p->Sk, ks, st);
 }
 
 }  // namespace fb
