@@ -1,18 +1,21 @@
 // Backward FlashBias attention for sm_100a.
 //
-// One CTA owns one tile of 128 keys of one (batch, head): K|packed k_bias and V stay resident in
-// shared memory, the dK|dk_bias and dV accumulators stay resident in tensor memory (no atomics on
-// them), and the CTA walks the query tiles that see those keys:
-//   warp 12     TMA producer: K|Kb|Kc, V once; then Q|Qb and dO tiles through a 2-stage ring.
-//   warps 13-16 MMA issuers (one thread each, one per warp scheduler), per query tile:
+// One CTA (512 threads) owns one tile of 128 keys of one (batch, head): K (and the (hi, lo) split of k*scale
+// when the scale is not a power of two), the packed k_bias tiles and V stay resident in shared memory, the
+// dK|dk_bias and dV accumulators stay resident in tensor memory (no atomics on them), and the CTA walks the
+// query tiles that see those keys:
+//   warp 12     TMA producer: resident tiles once, then Q|Qb|dO tiles through a 2- or 3-stage ring; the same
+//               thread issues the dQ | dQb MMAs.
+//   warps 13-15 MMA issuers (one thread each, every warp on its own warp scheduler), per query tile:
 //                 13: S  = [Q|Qb].[K|Kb]^T      dP = dO.V^T                     (TMEM, fresh)
 //                 14: dV += P^T.dO              15: dK|dKb += dS^T.[Q|Qb]       (TMEM, accumulated)
-//                 16: dQ|dQb = dS.[K|Kc]                                        (TMEM, fresh)
-//   warps 0-7   two warpgroups, each thread owns one query row (TMEM lane) and half of the key
-//               columns: P = exp2(S*scale*log2e - lse*log2e), dS = P*(dP - delta), both rounded to
-//               16 bits and written to shared memory as operand tiles.
-//   warps 8-11  drain warpgroup: the dQ|dQb tile is read from TMEM and added to fp32 accumulators in
-//               global memory with vector reductions.
+//                 12: dQ|dQb = dS.[K|Kc]                                        (TMEM, fresh, two accumulators)
+//   warps 0-7   two compute warpgroups, each thread owns one query row (TMEM lane) and half of the key
+//               columns: S and dP go to registers at once (releasing them for the next tile's MMAs),
+//               P = exp2(S*c - lse*log2e), dS = P*(dP - delta), both rounded to 16 bits and, once the previous
+//               tile's products have released them, written to shared memory as operand tiles.
+//   warps 8-11  drain warpgroup: the dQ|dQb tile goes from TMEM through a shared-memory staging tile into fp32
+//               accumulators in global memory with one bulk reduction each.
 // dQ is the only quantity that crosses CTAs (every key tile contributes to every query row), hence
 // the fp32 accumulators; a final pass scales and rounds them.  P and dS are read by the tensor core
 // both "as stored" and transposed, which is only a different shared-memory descriptor.
@@ -36,7 +39,9 @@ struct BwdArgs {
   const float* delta;
   int64_t lse_stride_bh;
   float* dq_acc;   // (B, Sq, H, D) fp32
-  float* dqb_acc;  // (Bq, Hq, nq_tiles * 128, R) fp32
+  float* dqb_acc;  // (slots, Bq, Hq, nq_tiles * 128, R) fp32
+  int dqb_slots;   // copies of the dq_bias accumulator; (batch, head) pairs that share a factor use different ones
+  int64_t dqb_slot_stride;  // floats per copy
   float* dkb_acc;  // (Bk, Sk, Hk, R) fp32
   void* dk;
   void* dv;
@@ -470,7 +475,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           for (int g = 0; g < 4; ++g) rsum[g] = s_rowsum[g * 128 + row];
           const int bq = a.bq_bcast ? 0 : b, hq = a.hq_bcast ? 0 : h;
           // accumulator laid out (Bq, Hq, query rows padded to whole tiles, R): a tile's rows are contiguous
-          float* tileb = a.dqb_acc + (((int64_t)bq * a.Hq + hq) * a.nq_tiles + (i_begin + it)) * (128 * a.R);
+          float* tileb = a.dqb_acc + (bh % a.dqb_slots) * a.dqb_slot_stride +
+                         (((int64_t)bq * a.Hq + hq) * a.nq_tiles + (i_begin + it)) * (128 * a.R);
           float* stgb = reinterpret_cast<float*>(smem + Cfg::OFF_STG + 128 * D * 4) + row * a.R;
           const int used = 2 * a.R;  // (hi, lo) column groups of the centred factor
 #pragma unroll 1
@@ -507,7 +513,9 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             if (RP && !FB_DBG(16)) {
               const int bq = a.bq_bcast ? 0 : b, hq = a.hq_bcast ? 0 : h;
               bulk_reduce_add_f32(
-                  a.dqb_acc + (((int64_t)bq * a.Hq + hq) * a.nq_tiles + (i_begin + it)) * (128 * a.R), sStgB,
+                  a.dqb_acc + (bh % a.dqb_slots) * a.dqb_slot_stride +
+                      (((int64_t)bq * a.Hq + hq) * a.nq_tiles + (i_begin + it)) * (128 * a.R),
+                  sStgB,
                   128 * a.R * 4);
             }
             bulk_commit_group();
@@ -755,7 +763,8 @@ extern "C" int fb_debug_trace_bwd(long long* out, int n) {
 namespace fb {
 #endif
 int store_factor_grads_from(const fb_params* p, float* dqb, float* dkb, cudaStream_t st,
-                            int64_t dqb_head_major_rows = 0);  // fb_general.cu
+                            int64_t dqb_head_major_rows = 0, int dqb_slots = 1,
+                            int64_t dqb_slot_stride = 0);  // fb_general.cu
 
 static bool rows_16b_ok(const void* ptr, const int64_t* st) {
   if (reinterpret_cast<uintptr_t>(ptr) & 15) return false;
@@ -766,6 +775,8 @@ static bool rows_16b_ok(const void* ptr, const int64_t* st) {
 
 struct BwdWs {
   size_t off_qpack, off_kpack, off_kcenter, off_qs, off_dq, off_dqb, off_dkb, total, zero_bytes;
+  int dqb_slots;
+  size_t dqb_slot_bytes;
 };
 static BwdWs bwd_layout(const fb_params* p, const PackPlan& plan) {
   BwdWs w;
@@ -776,8 +787,13 @@ static BwdWs bwd_layout(const fb_params* p, const PackPlan& plan) {
   w.off_dq = w.off_qs + plan.qs_bytes;
   // query rows padded to whole tiles: the bulk reductions of the backward write whole [128][D] tiles
   const size_t dq = round256((size_t)p->B * ((p->Sq + 127) / 128) * 128 * p->H * p->D * 4);
-  // (Bq, Hq, query rows padded to whole tiles, R): a query tile's rows are contiguous for the bulk reduction
-  const size_t dqb = p->R ? round256((size_t)plan.Bq * plan.Hq * ((p->Sq + 127) / 128) * 128 * p->R * 4) : 0;
+  // (Bq, Hq, query rows padded to whole tiles, R): a query tile's rows are contiguous for the bulk reduction.
+  // When the factor is shared by several (batch, head) pairs they would all add into the same addresses; up to
+  // 64 copies spread them, the final store sums the copies.
+  const int64_t sharing = (int64_t)(p->B / plan.Bq) * (p->H / plan.Hq);
+  w.dqb_slots = p->R ? (int)(sharing < 64 ? sharing : 64) : 1;
+  w.dqb_slot_bytes = p->R ? round256((size_t)plan.Bq * plan.Hq * ((p->Sq + 127) / 128) * 128 * p->R * 4) : 0;
+  const size_t dqb = w.dqb_slot_bytes * w.dqb_slots;
   const size_t dkb = p->R ? round256((size_t)plan.Bk * p->Sk * plan.Hk * p->R * 4) : 0;
   w.off_dqb = w.off_dq + dq;
   w.off_dkb = w.off_dqb + dqb;
@@ -886,6 +902,8 @@ static int launch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t s
   a.lse_stride_bh = p->lse_stride_bh;
   a.dq_acc = reinterpret_cast<float*>(ws + w.off_dq);
   a.dqb_acc = reinterpret_cast<float*>(ws + w.off_dqb);
+  a.dqb_slots = w.dqb_slots;
+  a.dqb_slot_stride = (int64_t)(w.dqb_slot_bytes / 4);
   a.dkb_acc = reinterpret_cast<float*>(ws + w.off_dkb);
   a.dk = p->dk;
   a.dv = p->dv;
@@ -921,7 +939,9 @@ static int launch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t s
       p->softmax_scale, Cfg::STAGED ? 1 : 0);
   note_launch();
   if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
-  if (p->R > 0) return store_factor_grads_from(p, a.dqb_acc, a.dkb_acc, st, (int64_t)a.nq_tiles * 128);
+  if (p->R > 0)
+    return store_factor_grads_from(p, a.dqb_acc, a.dkb_acc, st, (int64_t)a.nq_tiles * 128, a.dqb_slots,
+                                   a.dqb_slot_stride);
   return 0;
   }
 }

@@ -325,9 +325,11 @@ __global__ void __launch_bounds__(kWarps * 32) bwd_dkv_general_kernel(const fb_p
 }
 
 // fp32 accumulator -> 16-bit gradient tensor with the factor's own strides.  The accumulator is addressed
-// (b, h, s, r) through element strides (ab, ah, as): (Bx, S, Hx, R) or head-major with padded rows.
+// (b, h, s, r) through element strides (ab, ah, as): (Bx, S, Hx, R) or head-major with padded rows; `slots`
+// copies at distance `slot_stride` are summed.
 template <typename T>
 __global__ void factor_grad_store_kernel(const float* __restrict__ acc, int64_t ab, int64_t ah, int64_t as,
+                                         int slots, int64_t slot_stride,
                                          T* __restrict__ out, int Bx, int S, int Hx, int R, int64_t sb, int64_t sh,
                                          int64_t ss) {
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -337,7 +339,10 @@ __global__ void factor_grad_store_kernel(const float* __restrict__ acc, int64_t 
   const int h = (int)((idx / R) % Hx);
   const int s = (int)((idx / ((int64_t)R * Hx)) % S);
   const int b = (int)(idx / ((int64_t)R * Hx * S));
-  out[b * sb + h * sh + s * ss + r] = from_f32<T>(acc[b * ab + h * ah + s * as + r]);
+  const float* src = acc + b * ab + h * ah + s * as + r;
+  float v = 0.f;
+  for (int e = 0; e < slots; ++e) v += src[e * slot_stride];
+  out[b * sb + h * sh + s * ss + r] = from_f32<T>(v);
 }
 
 size_t bwd_general_workspace(const fb_params* p) {
@@ -350,31 +355,34 @@ size_t bwd_general_workspace(const fb_params* p) {
 
 template <typename T>
 static int launch_store_factor_grads(const fb_params* p, float* dqb, float* dkb, cudaStream_t st,
-                                     int64_t dqb_rows) {
+                                     int64_t dqb_rows, int dqb_slots, int64_t dqb_slot_stride) {
   const FactorAcc fa = factor_acc(*p);
   const int64_t nq = (int64_t)fa.Bq * p->Sq * fa.Hq * p->R, nk = (int64_t)fa.Bk * p->Sk * fa.Hk * p->R;
   const int64_t R = p->R;
   if (dqb_rows > 0)  // (Bq, Hq, dqb_rows, R)
     factor_grad_store_kernel<T><<<(unsigned)((nq + 255) / 256), 256, 0, st>>>(
-        dqb, fa.Hq * dqb_rows * R, dqb_rows * R, R, reinterpret_cast<T*>(p->dq_bias), fa.Bq, p->Sq, fa.Hq, p->R,
+        dqb, fa.Hq * dqb_rows * R, dqb_rows * R, R, dqb_slots, dqb_slot_stride, reinterpret_cast<T*>(p->dq_bias), fa.Bq, p->Sq, fa.Hq, p->R,
         p->dq_bias_stride[0], p->dq_bias_stride[1], p->dq_bias_stride[2]);
   else  // (Bq, Sq, Hq, R)
     factor_grad_store_kernel<T><<<(unsigned)((nq + 255) / 256), 256, 0, st>>>(
-        dqb, (int64_t)p->Sq * fa.Hq * R, R, fa.Hq * R, reinterpret_cast<T*>(p->dq_bias), fa.Bq, p->Sq, fa.Hq, p->R,
+        dqb, (int64_t)p->Sq * fa.Hq * R, R, fa.Hq * R, 1, 0, reinterpret_cast<T*>(p->dq_bias), fa.Bq, p->Sq, fa.Hq, p->R,
         p->dq_bias_stride[0], p->dq_bias_stride[1], p->dq_bias_stride[2]);
   factor_grad_store_kernel<T><<<(unsigned)((nk + 255) / 256), 256, 0, st>>>(
-      dkb, (int64_t)p->Sk * fa.Hk * R, R, fa.Hk * R, reinterpret_cast<T*>(p->dk_bias), fa.Bk, p->Sk, fa.Hk, p->R,
+      dkb, (int64_t)p->Sk * fa.Hk * R, R, fa.Hk * R, 1, 0, reinterpret_cast<T*>(p->dk_bias), fa.Bk, p->Sk, fa.Hk, p->R,
       p->dk_bias_stride[0], p->dk_bias_stride[1], p->dk_bias_stride[2]);
   note_launch(2);
   return (int)cudaGetLastError();
 }
 
 // Round fp32 factor-gradient accumulators into dq_bias / dk_bias.  The accumulators have the un-expanded shape
-// (Bx, S, Hx, R); with dqb_head_major_rows > 0 the q-side one is (Bq, Hq, dqb_head_major_rows, R) instead.
+// (Bx, S, Hx, R); with dqb_head_major_rows > 0 the q-side one is dqb_slots copies of (Bq, Hq, dqb_head_major_rows, R)
+// instead, which are summed.
 int store_factor_grads_from(const fb_params* p, float* dqb, float* dkb, cudaStream_t st,
-                            int64_t dqb_head_major_rows) {
-  return p->dtype == FB_DTYPE_F16 ? launch_store_factor_grads<__half>(p, dqb, dkb, st, dqb_head_major_rows)
-                                  : launch_store_factor_grads<__nv_bfloat16>(p, dqb, dkb, st, dqb_head_major_rows);
+                            int64_t dqb_head_major_rows, int dqb_slots, int64_t dqb_slot_stride) {
+  return p->dtype == FB_DTYPE_F16
+             ? launch_store_factor_grads<__half>(p, dqb, dkb, st, dqb_head_major_rows, dqb_slots, dqb_slot_stride)
+             : launch_store_factor_grads<__nv_bfloat16>(p, dqb, dkb, st, dqb_head_major_rows, dqb_slots,
+                                                        dqb_slot_stride);
 }
 
 int launch_fwd_general(const fb_params* p, cudaStream_t st) {
@@ -424,7 +432,7 @@ int launch_bwd_general(const fb_params* p, cudaStream_t st) {
   if (e != cudaSuccess) return (int)e;
   if (p->R <= 0) return 0;
   const FactorAcc fa = factor_acc(*p);
-  return store_factor_grads_from(p, fa.dqb, fa.dkb, st, 0);
+  return store_factor_grads_from(p, fa.dqb, fa.dkb, st, 0, 1, 0);
 }
 
 }  // namespace fb

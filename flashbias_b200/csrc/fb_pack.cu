@@ -55,6 +55,7 @@ bool plan_pack(const fb_params* p, PackPlan* plan, bool for_bwd) {
   return true;
 }
 
+// One thread per (b, h, s) row; the packed row is built 8 columns (one 16-byte store) at a time.
 template <typename T>
 __global__ void __launch_bounds__(256) pack_factor_kernel(const T* __restrict__ src, int64_t sb, int64_t sh, int64_t ss,
                                                           int Bx, int Hx, int S, int R, int RP, int RC, float mult,
@@ -67,30 +68,43 @@ __global__ void __launch_bounds__(256) pack_factor_kernel(const T* __restrict__ 
   const int h = (int)((idx / S) % Hx);
   const int b = (int)(idx / ((int64_t)S * Hx));
   const T* in = src + b * sb + h * sh + s * ss;
-  T* out = dst + idx * RP;
-  for (int c = 0; c < RP; ++c) {
-    if (c < R) {
-      const float x = to_f32(in[c]);
-      const T y = from_f32<T>(x * mult);  // mult is 1 or a power of two: exact unless it overflows
-      if (!isfinite(to_f32(y)) && isfinite(x) && status) atomicExch(status, FB_DEV_FACTOR_OVERFLOW);
-      out[c] = y;
-    } else {
-      out[c] = from_f32<T>(0.f);
+  bool overflow = false;
+  for (int c0 = 0; c0 < RP; c0 += 8) {
+    uint4 w = make_uint4(0u, 0u, 0u, 0u);
+    T* y = reinterpret_cast<T*>(&w);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int c = c0 + i;
+      if (c < R) {
+        const float x = to_f32(in[c]);
+        y[i] = from_f32<T>(x * mult);  // mult is 1 or a power of two: exact unless it overflows
+        overflow |= !isfinite(to_f32(y[i])) && isfinite(x);
+      }
     }
+    *reinterpret_cast<uint4*>(dst + idx * RP + c0) = w;
   }
+  if (overflow && status) atomicExch(status, FB_DEV_FACTOR_OVERFLOW);
   if (dst_centered) {
     // k-side factor minus the factor of the middle key of its group of 32 keys: small-magnitude copy used
-    // for dq_bias = dS.k_bias (the removed constant is re-applied in fp32 through the row sum of dS)
+    // for dq_bias = dS.k_bias (the removed constant is re-applied in fp32 through the row sum of dS);
+    // two-term split: columns [0,R) hi, [R,2R) lo, zero beyond
     int s0 = (s & ~31) + 16;
     if (s0 > S - 1) s0 = S - 1;
     const T* in0 = src + b * sb + h * sh + (int64_t)s0 * ss;
-    T* outc = dst_centered + idx * RC;
-    for (int c = 2 * R; c < RC; ++c) outc[c] = from_f32<T>(0.f);
-    for (int c = 0; c < R; ++c) {  // two-term split: columns [0,R) hi, [R,2R) lo
-      const float x = to_f32(in[c]) - to_f32(in0[c]);
-      const T hi = from_f32<T>(x);
-      outc[c] = hi;
-      outc[R + c] = from_f32<T>(x - to_f32(hi));
+    for (int c0 = 0; c0 < RC; c0 += 8) {
+      uint4 w = make_uint4(0u, 0u, 0u, 0u);
+      T* y = reinterpret_cast<T*>(&w);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int c = c0 + i;
+        if (c < 2 * R) {
+          const int cc = c < R ? c : c - R;
+          const float x = to_f32(in[cc]) - to_f32(in0[cc]);
+          const T hi = from_f32<T>(x);
+          y[i] = c < R ? hi : from_f32<T>(x - to_f32(hi));
+        }
+      }
+      *reinterpret_cast<uint4*>(dst_centered + idx * RC + c0) = w;
     }
   }
 }
