@@ -42,7 +42,9 @@ struct BwdArgs {
   float* dqb_acc;  // (slots, Bq, Hq, nq_tiles * 128, R) fp32
   int dqb_slots;   // copies of the dq_bias accumulator; (batch, head) pairs that share a factor use different ones
   int64_t dqb_slot_stride;  // floats per copy
-  float* dkb_acc;  // (Bk, Sk, Hk, R) fp32
+  float* dkb_acc;  // (slots, Bk, Hk, nk_tiles * 128, R) fp32
+  int dkb_slots;
+  int64_t dkb_slot_stride;
   void* dk;
   void* dv;
   int64_t dk_stride[3], dv_stride[3];
@@ -683,19 +685,28 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     }
     if (RP && wg == 0) {
+      // dk_bias tile of this CTA: staged [128][R] in the (now idle) P tile, one bulk reduction into the accumulator
+      // (other (batch, head) pairs add to the same rows when the factor is shared)
       const int bk = a.bk_bcast ? 0 : b, hk = a.hk_bcast ? 0 : h;
-      float* dst = a.dkb_acc + (((int64_t)bk * a.Sk + krow) * a.Hk + hk) * a.R;
+      float* stg = reinterpret_cast<float*>(smem + Cfg::OFF_P) + row * a.R;
       const int used = a.R;
 #pragma unroll 1
       for (int c0 = 0; c0 < RPX && c0 < used; c0 += 16) {
         uint32_t r[16];
         tmem_ld16(tmem + Cfg::T_DKB + lane_off + c0, r);
         tmem_wait_ld(r);
-        if (krow < a.Sk) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
-            if (c0 + i < used) atomicAdd(dst + c0 + i, __uint_as_float(r[i]) * a.dkb_scale);
-        }
+        for (int i = 0; i < 16; ++i)
+          if (c0 + i < used) stg[c0 + i] = __uint_as_float(r[i]) * a.dkb_scale;
+      }
+      fence_proxy_async_smem();
+      asm volatile("bar.sync 4, 128;" ::: "memory");  // warpgroup 0 only
+      if (threadIdx.x == 0) {
+        bulk_reduce_add_f32(a.dkb_acc + (bh % a.dkb_slots) * a.dkb_slot_stride +
+                                (((int64_t)bk * a.Hk + hk) * a.nk_tiles + kt) * (128 * a.R),
+                            sP, 128 * a.R * 4);
+        bulk_commit_group();
+        bulk_wait_group0();
       }
     }
   } else {
@@ -762,9 +773,6 @@ extern "C" int fb_debug_trace_bwd(long long* out, int n) {
 }
 namespace fb {
 #endif
-int store_factor_grads_from(const fb_params* p, float* dqb, float* dkb, cudaStream_t st,
-                            int64_t dqb_head_major_rows = 0, int dqb_slots = 1,
-                            int64_t dqb_slot_stride = 0);  // fb_general.cu
 
 static bool rows_16b_ok(const void* ptr, const int64_t* st) {
   if (reinterpret_cast<uintptr_t>(ptr) & 15) return false;
@@ -775,8 +783,8 @@ static bool rows_16b_ok(const void* ptr, const int64_t* st) {
 
 struct BwdWs {
   size_t off_qpack, off_kpack, off_kcenter, off_qs, off_dq, off_dqb, off_dkb, total, zero_bytes;
-  int dqb_slots;
-  size_t dqb_slot_bytes;
+  int dqb_slots, dkb_slots;
+  size_t dqb_slot_bytes, dkb_slot_bytes;
 };
 static BwdWs bwd_layout(const fb_params* p, const PackPlan& plan) {
   BwdWs w;
@@ -794,7 +802,10 @@ static BwdWs bwd_layout(const fb_params* p, const PackPlan& plan) {
   w.dqb_slots = p->R ? (int)(sharing < 64 ? sharing : 64) : 1;
   w.dqb_slot_bytes = p->R ? round256((size_t)plan.Bq * plan.Hq * ((p->Sq + 127) / 128) * 128 * p->R * 4) : 0;
   const size_t dqb = w.dqb_slot_bytes * w.dqb_slots;
-  const size_t dkb = p->R ? round256((size_t)plan.Bk * p->Sk * plan.Hk * p->R * 4) : 0;
+  const int64_t ksharing = (int64_t)(p->B / plan.Bk) * (p->H / plan.Hk);
+  w.dkb_slots = p->R ? (int)(ksharing < 64 ? ksharing : 64) : 1;
+  w.dkb_slot_bytes = p->R ? round256((size_t)plan.Bk * plan.Hk * ((p->Sk + 127) / 128) * 128 * p->R * 4) : 0;
+  const size_t dkb = w.dkb_slot_bytes * w.dkb_slots;
   w.off_dqb = w.off_dq + dq;
   w.off_dkb = w.off_dqb + dqb;
   w.total = w.off_dkb + dkb;
@@ -905,6 +916,8 @@ static int launch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t s
   a.dqb_slots = w.dqb_slots;
   a.dqb_slot_stride = (int64_t)(w.dqb_slot_bytes / 4);
   a.dkb_acc = reinterpret_cast<float*>(ws + w.off_dkb);
+  a.dkb_slots = w.dkb_slots;
+  a.dkb_slot_stride = (int64_t)(w.dkb_slot_bytes / 4);
   a.dk = p->dk;
   a.dv = p->dv;
   for (int i = 0; i < 3; ++i) {
@@ -940,8 +953,9 @@ static int launch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t s
   note_launch();
   if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
   if (p->R > 0)
-    return store_factor_grads_from(p, a.dqb_acc, a.dkb_acc, st, (int64_t)a.nq_tiles * 128, a.dqb_slots,
-                                   a.dqb_slot_stride);
+    return store_factor_grads_from(p, a.dqb_acc, a.dkb_acc, st,
+                                   {(int64_t)a.nq_tiles * 128, a.dqb_slots, a.dqb_slot_stride},
+                                   {(int64_t)a.nk_tiles * 128, a.dkb_slots, a.dkb_slot_stride});
   return 0;
   }
 }

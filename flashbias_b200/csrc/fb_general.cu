@@ -354,35 +354,35 @@ size_t bwd_general_workspace(const fb_params* p) {
 }
 
 template <typename T>
+static void launch_one_factor_store(const float* acc, FactorAccLayout l, T* out, int Bx, int S, int Hx, int R,
+                                    const int64_t* stride, cudaStream_t st) {
+  const int64_t n = (int64_t)Bx * S * Hx * R;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  if (l.rows > 0)  // (slots, Bx, Hx, rows, R)
+    factor_grad_store_kernel<T><<<blocks, 256, 0, st>>>(acc, Hx * l.rows * R, l.rows * R, R, l.slots, l.slot_stride,
+                                                        out, Bx, S, Hx, R, stride[0], stride[1], stride[2]);
+  else  // (Bx, S, Hx, R)
+    factor_grad_store_kernel<T><<<blocks, 256, 0, st>>>(acc, (int64_t)S * Hx * R, R, (int64_t)Hx * R, 1, 0, out, Bx, S,
+                                                        Hx, R, stride[0], stride[1], stride[2]);
+}
+
+template <typename T>
 static int launch_store_factor_grads(const fb_params* p, float* dqb, float* dkb, cudaStream_t st,
-                                     int64_t dqb_rows, int dqb_slots, int64_t dqb_slot_stride) {
+                                     FactorAccLayout ql, FactorAccLayout kl) {
   const FactorAcc fa = factor_acc(*p);
-  const int64_t nq = (int64_t)fa.Bq * p->Sq * fa.Hq * p->R, nk = (int64_t)fa.Bk * p->Sk * fa.Hk * p->R;
-  const int64_t R = p->R;
-  if (dqb_rows > 0)  // (Bq, Hq, dqb_rows, R)
-    factor_grad_store_kernel<T><<<(unsigned)((nq + 255) / 256), 256, 0, st>>>(
-        dqb, fa.Hq * dqb_rows * R, dqb_rows * R, R, dqb_slots, dqb_slot_stride, reinterpret_cast<T*>(p->dq_bias), fa.Bq, p->Sq, fa.Hq, p->R,
-        p->dq_bias_stride[0], p->dq_bias_stride[1], p->dq_bias_stride[2]);
-  else  // (Bq, Sq, Hq, R)
-    factor_grad_store_kernel<T><<<(unsigned)((nq + 255) / 256), 256, 0, st>>>(
-        dqb, (int64_t)p->Sq * fa.Hq * R, R, fa.Hq * R, 1, 0, reinterpret_cast<T*>(p->dq_bias), fa.Bq, p->Sq, fa.Hq, p->R,
-        p->dq_bias_stride[0], p->dq_bias_stride[1], p->dq_bias_stride[2]);
-  factor_grad_store_kernel<T><<<(unsigned)((nk + 255) / 256), 256, 0, st>>>(
-      dkb, (int64_t)p->Sk * fa.Hk * R, R, fa.Hk * R, 1, 0, reinterpret_cast<T*>(p->dk_bias), fa.Bk, p->Sk, fa.Hk, p->R,
-      p->dk_bias_stride[0], p->dk_bias_stride[1], p->dk_bias_stride[2]);
+  launch_one_factor_store<T>(dqb, ql, reinterpret_cast<T*>(p->dq_bias), fa.Bq, p->Sq, fa.Hq, p->R,
+                             p->dq_bias_stride, st);
+  launch_one_factor_store<T>(dkb, kl, reinterpret_cast<T*>(p->dk_bias), fa.Bk, p->Sk, fa.Hk, p->R,
+                             p->dk_bias_stride, st);
   note_launch(2);
   return (int)cudaGetLastError();
 }
 
-// Round fp32 factor-gradient accumulators into dq_bias / dk_bias.  The accumulators have the un-expanded shape
-// (Bx, S, Hx, R); with dqb_head_major_rows > 0 the q-side one is dqb_slots copies of (Bq, Hq, dqb_head_major_rows, R)
-// instead, which are summed.
-int store_factor_grads_from(const fb_params* p, float* dqb, float* dkb, cudaStream_t st,
-                            int64_t dqb_head_major_rows, int dqb_slots, int64_t dqb_slot_stride) {
-  return p->dtype == FB_DTYPE_F16
-             ? launch_store_factor_grads<__half>(p, dqb, dkb, st, dqb_head_major_rows, dqb_slots, dqb_slot_stride)
-             : launch_store_factor_grads<__nv_bfloat16>(p, dqb, dkb, st, dqb_head_major_rows, dqb_slots,
-                                                        dqb_slot_stride);
+// Round the fp32 factor-gradient accumulators into dq_bias / dk_bias.
+int store_factor_grads_from(const fb_params* p, float* dqb, float* dkb, cudaStream_t st, FactorAccLayout q_layout,
+                            FactorAccLayout k_layout) {
+  return p->dtype == FB_DTYPE_F16 ? launch_store_factor_grads<__half>(p, dqb, dkb, st, q_layout, k_layout)
+                                  : launch_store_factor_grads<__nv_bfloat16>(p, dqb, dkb, st, q_layout, k_layout);
 }
 
 int launch_fwd_general(const fb_params* p, cudaStream_t st) {
@@ -432,7 +432,7 @@ int launch_bwd_general(const fb_params* p, cudaStream_t st) {
   if (e != cudaSuccess) return (int)e;
   if (p->R <= 0) return 0;
   const FactorAcc fa = factor_acc(*p);
-  return store_factor_grads_from(p, fa.dqb, fa.dkb, st, 0, 1, 0);
+  return store_factor_grads_from(p, fa.dqb, fa.dkb, st);
 }
 
 }  // namespace fb

@@ -60,6 +60,17 @@ int launch_bwd_sm100(const fb_params* p, const PackPlan& plan, cudaStream_t st);
 
 inline size_t round256(size_t x) { return (x + 255) & ~size_t(255); }
 
+// fp32 factor-gradient accumulators.  Default shape: the un-expanded (Bx, S, Hx, R).  The tensor-core backward
+// uses `slots` copies (summed by the final store) of a head-major (Bx, Hx, rows, R) array with rows padded to
+// whole 128-row tiles, so that a tile's rows are contiguous for a bulk reduction.
+struct FactorAccLayout {
+  int64_t rows;         // 0: default shape
+  int slots;            // copies to sum
+  int64_t slot_stride;  // floats between copies
+};
+int store_factor_grads_from(const fb_params* p, float* dqb, float* dkb, cudaStream_t st,
+                            FactorAccLayout q_layout = {0, 1, 0}, FactorAccLayout k_layout = {0, 1, 0});
+
 // ---- instrumentation (fb_api.cu) ----------------------------------------------------------------
 // Every kernel launch of the library is counted; while profiling is armed for a kernel class, a pair
 // of CUDA events is recorded around each launch of that class on the launching stream.
