@@ -189,6 +189,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::OFF_BAR + 104);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) FB_TRACE_MARK(0, 20);
   const int BH = a.B * a.H;
   int kt, bh;
   if (a.causal) {  // key tile 0 sees the most query tiles: heaviest first
@@ -203,7 +204,19 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int i_begin = a.causal ? kt : 0;  // first query tile with a row >= k0
   const int n_it = a.nq_tiles - i_begin;  // may be <= 0 when Sq < Sk under causal masking
 
-  if (warp == 13) {
+  // producer thread only: one stage of the query-tile ring
+  const int hq = a.hq_bcast ? 0 : h, bq = a.bq_bcast ? 0 : b;
+  auto load_tile = [&](int it) {
+    const int st = it % Cfg::NSTAGE;
+    const uint32_t base = sStage + st * Cfg::STAGE_BYTES;
+    mbar_expect_tx(qdo_full + 8 * st, Cfg::STAGE_BYTES);
+    const int q0 = (i_begin + it) * 128;
+    tma_tile_bwd<D>(base, &tmQ, qdo_full + 8 * st, q0, h, b);
+    if (RP) tma_tile_bwd<RPX>(base + Cfg::OFF_QB, &tmQb, qdo_full + 8 * st, q0, hq, bq);
+    tma_tile_bwd<D>(base + Cfg::OFF_DO, &tmDO, qdo_full + 8 * st, q0, h, b);
+  };
+
+  if (warp == 12) {
     if (lane == 0) {
       *abort_flag = 0;
       mbar_init(kv_full, 1);
@@ -223,8 +236,23 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                                            // different times
       }
       mbar_fence_init();
+      if (n_it > 0) {
+        // the first loads start before the rest of the CTA has finished its set-up
+        const int hk = a.hk_bcast ? 0 : h, bk = a.bk_bcast ? 0 : b;
+        mbar_expect_tx(kv_full, Cfg::KV_BYTES);
+        tma_tile_bwd<D>(sK, &tmK, kv_full, k0, h, b);
+        if (NQ == 2) {
+          tma_tile_bwd<D>(sKs, &tmKs, kv_full, k0, h, b);
+          tma_tile_bwd<D>(sKs + Cfg::D_BYTES, &tmKs, kv_full, k0, h, b, D);
+        }
+        if (RP) tma_tile_bwd<RPX>(sKb, &tmKb, kv_full, k0, hk, bk);
+        tma_tile_bwd<D>(sV, &tmV, kv_full, k0, h, b);
+        load_tile(0);
+        if (RP) tma_tile_bwd<Cfg::RCX>(sKc, &tmKc, kv_full, k0, hk, bk);
+        for (int it = 1; it < Cfg::NSTAGE && it < n_it; ++it) load_tile(it);
+      }
     }
-    __syncwarp();
+  } else if (warp == 13) {
     tmem_alloc(smem_u32(tmem_slot), 512);
     tmem_relinquish();
   }
@@ -232,6 +260,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
+  if (threadIdx.x == 0) FB_TRACE_MARK(0, 21);
 
   // 512 threads start with 128 registers each; the two compute warpgroups hold a whole tile of S and dP in
   // registers and take 176, the drain warpgroup and the producer/issuer warpgroup keep 80.  Each warpgroup
@@ -241,27 +270,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (warp == 12) {
     // ------------------------------------------------------------------ TMA producer, dQ | dQb chain
     if (lane == 0 && n_it > 0) {
-      const int hq = a.hq_bcast ? 0 : h, bq = a.bq_bcast ? 0 : b;
-      const int hk = a.hk_bcast ? 0 : h, bk = a.bk_bcast ? 0 : b;
-      mbar_expect_tx(kv_full, Cfg::KV_BYTES);
-      tma_tile_bwd<D>(sK, &tmK, kv_full, k0, h, b);
-      if (NQ == 2) {
-        tma_tile_bwd<D>(sKs, &tmKs, kv_full, k0, h, b);
-        tma_tile_bwd<D>(sKs + Cfg::D_BYTES, &tmKs, kv_full, k0, h, b, D);
-      }
-      if (RP) tma_tile_bwd<RPX>(sKb, &tmKb, kv_full, k0, hk, bk);
-      if (RP) tma_tile_bwd<Cfg::RCX>(sKc, &tmKc, kv_full, k0, hk, bk);
-      tma_tile_bwd<D>(sV, &tmV, kv_full, k0, h, b);
-      auto load_tile = [&](int it) {
-        const int st = it % Cfg::NSTAGE;
-        const uint32_t base = sStage + st * Cfg::STAGE_BYTES;
-        mbar_expect_tx(qdo_full + 8 * st, Cfg::STAGE_BYTES);
-        const int q0 = (i_begin + it) * 128;
-        tma_tile_bwd<D>(base, &tmQ, qdo_full + 8 * st, q0, h, b);
-        if (RP) tma_tile_bwd<RPX>(base + Cfg::OFF_QB, &tmQb, qdo_full + 8 * st, q0, hq, bq);
-        tma_tile_bwd<D>(base + Cfg::OFF_DO, &tmDO, qdo_full + 8 * st, q0, h, b);
-      };
-      for (int it = 0; it < Cfg::NSTAGE && it < n_it; ++it) load_tile(it);
       // The same thread issues the dQ | dQb products: they become due when a query tile's P/dS are written,
       // the next load when the other chains have finished with that tile's stage -- in this order, every tile.
       constexpr uint32_t idQD = instr_desc(kBf16, false, true, 128, D);             // dQ: A K-major, B MN-major
@@ -525,7 +533,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
         }
       }
-      if (Cfg::STAGED && warp == 8 && lane == 0) bulk_wait_group0();  // reductions complete before the CTA exits
+      // (the last reduction's shared-memory reads were awaited above; its global side completes with the kernel)
     }
   } else if (n_it > 0) {
     // ------------------------------------------------------------------ compute warpgroups (warps 0-7)
@@ -652,6 +660,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // the dV and dK|dKb accumulators are final once every MMA of the CTA has completed
     mbar_wait(all_done, 0, abort_flag, a.status);
     tc_fence_after_sync();
+    if (threadIdx.x == 0) FB_TRACE_MARK(0, 22);
 
     // ---- epilogue: dV, dK (x scale), dKb (x scale, split terms folded)
     // the last dq_full phase covered every MMA of the CTA, so the accumulators are final
@@ -706,7 +715,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                                 (((int64_t)bk * a.Hk + hk) * a.nk_tiles + kt) * (128 * a.R),
                             sP, 128 * a.R * 4);
         bulk_commit_group();
-        bulk_wait_group0();
+        bulk_wait_group_read0();  // shared memory must stay until it is read; the global side completes with the kernel
       }
     }
   } else {
@@ -726,6 +735,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0) FB_TRACE_MARK(0, 23);
   if (warp == 13) {
     __syncwarp();
     tmem_dealloc(tmem, 512);
