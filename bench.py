@@ -258,17 +258,34 @@ def main():
     e2e_steps = max(3, min(args.steps, 10))
     dq_ = [torch.empty_like(t, device=dev) for t in host]
 
+    copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+
     def e2e_step():
+        # inputs come in on a copy stream (dO behind the forward's operands, so it lands under the forward), o goes
+        # back to the host on a second copy stream under the backward; every copy is inside the timed region
         nonlocal out_host
-        for dst, src in zip(dq_, host):
-            dst.copy_(src, non_blocking=True)
+        main = torch.cuda.current_stream()
+        copy_in.wait_stream(main)
+        with torch.cuda.stream(copy_in):
+            for dst, src in zip(dq_[:5], host[:5]):
+                dst.copy_(src, non_blocking=True)
+            ev_in = torch.cuda.Event()
+            ev_in.record()
+            dq_[5].copy_(host[5], non_blocking=True)
+            ev_do = torch.cuda.Event()
+            ev_do.record()
+        main.wait_event(ev_in)
         qq, kk, vv, qqb, kkb = (t.detach().requires_grad_(True) for t in dq_[:5])
         o = flash_bias_func(qq, kk, vv, qqb, kkb, None, w.causal, w.softmax_scale)
-        o.backward(dq_[5])
-        res = [o.detach(), qq.grad, kk.grad, vv.grad, qqb.grad, kkb.grad]
         if out_host is None:
-            out_host = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in res]
-        for dst, src in zip(out_host, res):
+            shapes = [o, qq, kk, vv, qqb, kkb]
+            out_host = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in shapes]
+        copy_out.wait_stream(main)
+        with torch.cuda.stream(copy_out):
+            out_host[0].copy_(o.detach(), non_blocking=True)
+        main.wait_event(ev_do)
+        o.backward(dq_[5])
+        for dst, src in zip(out_host[1:], (qq.grad, kk.grad, vv.grad, qqb.grad, kkb.grad)):
             dst.copy_(src, non_blocking=True)
         torch.cuda.synchronize()
 

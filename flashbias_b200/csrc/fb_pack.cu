@@ -44,6 +44,9 @@ bool plan_pack(const fb_params* p, PackPlan* plan, bool for_bwd) {
   }
   // the centred k-side copy of the backward holds a (hi, lo) pair: twice the rank
   plan->RP = pad_pow2_16(for_bwd ? 2 * p->R : p->R);
+  // backward at head_dim 32: factor tiles as wide as the Q/K tiles, so that [Q | Qb] and [K | Kc] are read as one
+  // MMA operand each (one product instead of two per 16 query rows / keys)
+  if (for_bwd && p->D == 32 && plan->RP < 32) plan->RP = 32;
   if (plan->RP > 64) return false;
   plan->q_bytes = round256((size_t)plan->Bq * plan->Hq * p->Sq * plan->RP * 2);
   plan->k_bytes = round256((size_t)plan->Bk * plan->Hk * p->Sk * plan->RP * 2);
