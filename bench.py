@@ -41,6 +41,14 @@ FULL_SIZES = {
     "pde": dict(B=2, H=8, S=32768, D=64),
     "pairformer": dict(B=1, H=16, S=1536, D=32, R=32),
 }
+# reduced cases for profiler captures (--profile-case): same kernels, inputs larger than L2, a few hundred MB at most
+PROFILE_SIZES = {
+    "generic": dict(B=2, H=4, S=1024, D=32, R=8),
+    "alibi": dict(B=1, H=16, S=4096, D=32),
+    "swin": dict(B=256, H=24, window=16, D=32, R=16),
+    "pde": dict(B=1, H=4, S=8192, D=64),
+    "pairformer": dict(B=1, H=16, S=1536, D=32, R=32),
+}
 # bounded CPU sample of each workload: (sizes of the sample, how it scales to the full workload)
 CPU_SAMPLE = {
     "generic": (dict(B=2, H=4, S=1024, D=32, R=8), "whole workload"),
@@ -166,6 +174,9 @@ def main():
     ap.add_argument("--workload", default="alibi", choices=sorted(FULL_SIZES))
     ap.add_argument("--impl", default="flashbias", choices=["flashbias", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-case", action="store_true",
+                    help="run only --steps forward+backward calls of a reduced case (for a profiler capture); "
+                         "prints no bench line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "flashbias" else args.warmup
 
@@ -188,6 +199,14 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     lib = _lib.load()
 
+    if args.profile_case:
+        w = make_workload(args.workload, **PROFILE_SIZES[args.workload]).to(dev)
+        q, k, v, qb, kb = (t.requires_grad_(True) for t in (w.q, w.k, w.v, w.q_bias, w.k_bias))
+        for _ in range(args.warmup + args.steps):
+            flash_bias_func(q, k, v, qb, kb, None, w.causal, w.softmax_scale).backward(w.do)
+        torch.cuda.synchronize()
+        print(json.dumps({"profile_case": args.workload, **PROFILE_SIZES[args.workload]}), flush=True)
+        return
     sizes = FULL_SIZES[args.workload]
     w = make_workload(args.workload, **sizes)
     sh = w.shape

@@ -181,7 +181,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                  sP = sbase + Cfg::OFF_P, sDS = sbase + Cfg::OFF_DS, sStg = sbase + Cfg::OFF_STG,
                  sStgB = sStg + 128 * D * 4;
   const uint32_t bar0 = sbase + Cfg::OFF_BAR;
-  const uint32_t kv_full = bar0, s_full = bar0 + 8, dp_full = bar0 + 16, sdp_read = bar0 + 24,
+  const uint32_t kv_full = bar0, dp_full = bar0 + 16, sdp_read = bar0 + 24,
                  dq_full = bar0 + 32 /*2*/, qdo_full = bar0 + 48 /*3*/, qdo_free = bar0 + 72 /*3*/,
                  all_done = bar0 + 112, pds_free = bar0 + 120, pds_ready = bar0 + 136 /*2*/,
                  dq_drained = bar0 + 152 /*2*/;
@@ -220,7 +220,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (lane == 0) {
       *abort_flag = 0;
       mbar_init(kv_full, 1);
-      mbar_init(s_full, 1);
       mbar_init(dp_full, 1);
       mbar_init(sdp_read, 8);  // every compute warp has S and dP of the tile in registers
       mbar_init(all_done, 4);  // one commit per issuing thread
@@ -263,10 +262,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (threadIdx.x == 0) FB_TRACE_MARK(0, 21);
 
   // 512 threads start with 128 registers each; the two compute warpgroups hold a whole tile of S and dP in
-  // registers and take 176, the drain warpgroup and the producer/issuer warpgroup keep 80.  Each warpgroup
+  // registers and take 192, the drain warpgroup and the producer/issuer warpgroup keep 64.  Each warpgroup
   // changes its budget at the head of its own branch.
   if (warp >= 12) {
-  setmaxnreg_dec<80>();
+  setmaxnreg_dec<64>();
   if (warp == 12) {
     // ------------------------------------------------------------------ TMA producer, dQ | dQb chain
     if (lane == 0 && n_it > 0) {
@@ -365,7 +364,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               umma_ss(tmem + Cfg::T_S, desc_at(kQ, so + kmajor_step<D>(s)),
                       desc_at(kK, t * Cfg::D_BYTES + kmajor_step<D>(s)), idS, (RP || t > 0 || s > 0) ? 1u : 0u);
           }
-          umma_commit(s_full);
 #pragma unroll
           for (int s = 0; s < D / 16; ++s)
             umma_ss(tmem + Cfg::T_DP, desc_at(kDO, so + kmajor_step<D>(s)), desc_at(kV, kmajor_step<D>(s)), idS,
@@ -422,7 +420,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   }
   } else if (warp >= 8) {
-    setmaxnreg_dec<80>();
+    setmaxnreg_dec<64>();
     // ------------------------------------------------------------------ drain warpgroup
     // dQ | dQb of each query tile from TMEM into the fp32 accumulators in global memory, off the critical path
     // of the warps that compute P and dS.  One thread per query row.
@@ -537,7 +535,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else if (n_it > 0) {
     // ------------------------------------------------------------------ compute warpgroups (warps 0-7)
-    setmaxnreg_inc<176>();
+    setmaxnreg_inc<192>();
     const int wg = warp >> 2;
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
@@ -569,6 +567,15 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
     float lse_raw, dlt;
     load_row_stats(0, lse_raw, dlt);
+    // The thread's 64 columns of S and of dP live in registers, as two chunks of 32.  Chunk 0 of a tile is fetched
+    // from tensor memory under the arithmetic of the previous tile's chunk 1; once chunk 1 has followed at the
+    // head of the tile, S and dP are released and the tensor core computes the next tile's under this tile's math.
+    uint32_t rs0[32], rd0[32], rs1[32], rd1[32];
+    const uint32_t tSl = tmem + Cfg::T_S + lane_off + wg * 64, tDl = tmem + Cfg::T_DP + lane_off + wg * 64;
+    mbar_wait(dp_full, 0, abort_flag, a.status);  // committed after the S and the dP products: covers both
+    tc_fence_after_sync();
+    tmem_ld32(tSl, rs0);
+    tmem_ld32(tDl, rd0);
 #pragma unroll 1
     for (int it = 0; it < n_it; ++it) {
       const int q0 = (i_begin + it) * 128;
@@ -577,17 +584,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const float lse2_cur = lse_raw == -INFINITY ? INFINITY : lse_raw * kLog2e, dlt_cur = dlt;
       const bool need_mask = (a.causal && k0 + 127 > q0) || (k0 + 128 > a.Sk);
       float ds_sum0 = 0.f, ds_sum1 = 0.f;  // fp32 row sums of dS over this thread's two 32-column groups
-      if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 14);
-      mbar_wait(s_full, it & 1, abort_flag, a.status);
-      mbar_wait(dp_full, it & 1, abort_flag, a.status);
-      tc_fence_after_sync();
       if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 0);
-      // The thread's 64 columns of S and of dP go to registers at once; tensor memory is then free for S and dP
-      // of the next query tile, which the tensor core computes under this tile's arithmetic.
-      uint32_t rs0[32], rd0[32], rs1[32], rd1[32];
-      const uint32_t tSl = tmem + Cfg::T_S + lane_off + wg * 64, tDl = tmem + Cfg::T_DP + lane_off + wg * 64;
-      tmem_ld32(tSl, rs0);
-      tmem_ld32(tDl, rd0);
       tmem_ld32(tSl + 32, rs1);
       tmem_ld32(tDl + 32, rd1);
       tmem_wait_ld(rs0);
@@ -631,6 +628,12 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       ds_sum0 = chunk(rs0, rd0, pk0, dk0, 0);
       if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 15);
       load_row_stats(it + 1, lse_raw, dlt);  // next tile's statistics: the loads complete under this tile's math
+      if (it + 1 < n_it) {  // chunk 0 of the next tile (its S and dP were issued when this tile was released)
+        mbar_wait(dp_full, (it + 1) & 1, abort_flag, a.status);
+        tc_fence_after_sync();
+        tmem_ld32(tSl, rs0);
+        tmem_ld32(tDl, rd0);
+      }
       if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 17);
       ds_sum1 = chunk(rs1, rd1, pk1, dk1, 1);
       if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 18);
