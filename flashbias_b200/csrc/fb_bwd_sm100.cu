@@ -568,7 +568,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     float lse_raw, dlt;
     load_row_stats(0, lse_raw, dlt);
     // The thread's 64 columns of S and of dP live in registers, as two chunks of 32.  Chunk 0 of a tile is fetched
-    // from tensor memory under the arithmetic of the previous tile's chunk 1; once chunk 1 has followed at the
+    // from tensor memory under the P/dS stores of the previous tile; once chunk 1 has followed at the
     // head of the tile, S and dP are released and the tensor core computes the next tile's under this tile's math.
     uint32_t rs0[32], rd0[32], rs1[32], rd1[32];
     const uint32_t tSl = tmem + Cfg::T_S + lane_off + wg * 64, tDl = tmem + Cfg::T_DP + lane_off + wg * 64;
@@ -628,15 +628,17 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       ds_sum0 = chunk(rs0, rd0, pk0, dk0, 0);
       if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 15);
       load_row_stats(it + 1, lse_raw, dlt);  // next tile's statistics: the loads complete under this tile's math
-      if (it + 1 < n_it) {  // chunk 0 of the next tile (its S and dP were issued when this tile was released)
+      if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 17);
+      ds_sum1 = chunk(rs1, rd1, pk1, dk1, 1);
+      if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 18);
+      if (it + 1 < n_it) {
+        // chunk 0 of the next tile (its S and dP were issued when this tile was released, long done by now):
+        // the fetch runs under the stores below
         mbar_wait(dp_full, (it + 1) & 1, abort_flag, a.status);
         tc_fence_after_sync();
         tmem_ld32(tSl, rs0);
         tmem_ld32(tDl, rd0);
       }
-      if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 17);
-      ds_sum1 = chunk(rs1, rd1, pk1, dk1, 1);
-      if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 18);
       // the dV, dK and dQ products of the previous query tile have read P and dS
       if (it >= 1) mbar_wait(pds_free, (it - 1) & 1, abort_flag, a.status);
 #pragma unroll
