@@ -105,3 +105,59 @@ def test_matches_reference_operator_semantics_default_scale_and_no_bias():
     o = flash_bias_func(q, k, v)  # no bias, default scale 1/sqrt(d), non-causal
     o_ref, _ = orc.attention_forward(q.cpu().float(), k.cpu().float(), v.cpu().float())
     check_close("nobias/o", o, o_ref, torch.float16)
+
+
+# Every tensor-core kernel variant (head_dim x packed rank x scale kind), ragged and causal shapes, broadcast
+# patterns of the factors: (B, H, Sq, Sk, D, R, causal, scale (None = 1/sqrt(D)), factor batch bcast, head bcast,
+# dtype, backward on the tensor path)
+VARIANTS = [
+    (2, 3, 384, 384, 32, 0, False, None, False, False, torch.bfloat16, True),
+    (1, 2, 300, 300, 32, 0, True, 0.25, False, False, torch.float16, True),     # power-of-two scale, ragged
+    (2, 2, 256, 384, 32, 8, False, 0.25, True, False, torch.bfloat16, True),    # factors shared over batch
+    (1, 4, 384, 256, 32, 12, True, None, False, True, torch.float16, True),     # causal Sq > Sk, shared over heads
+    (1, 2, 256, 256, 32, 24, False, None, True, True, torch.bfloat16, True),    # packed rank 64
+    (1, 2, 130, 400, 32, 4, True, None, False, False, torch.bfloat16, True),    # causal Sq < Sk: key tiles no query sees
+    (1, 2, 384, 384, 64, 0, True, None, False, False, torch.bfloat16, True),
+    (2, 2, 256, 256, 64, 12, False, None, False, True, torch.float16, True),    # head_dim 64, packed rank 32
+    (1, 2, 200, 456, 64, 5, False, 0.1, True, False, torch.bfloat16, True),     # scale not a power of two
+    (1, 2, 256, 256, 128, 8, False, None, False, False, torch.bfloat16, False),  # backward: shape-generic
+    (1, 2, 256, 256, 32, 40, False, None, False, False, torch.bfloat16, False),  # rank too large for the backward
+]
+
+
+@pytest.mark.parametrize("case", VARIANTS, ids=lambda c: "B%dH%dSq%dSk%dD%dR%d%s" % (c[0], c[1], c[2], c[3], c[4], c[5],
+                                                                                  "c" if c[6] else ""))
+def test_tensor_kernel_variants(case):
+    import ctypes as C
+    from flashbias_b200.flash_bias import _fill_common
+    B, H, Sq, Sk, D, R, causal, scale, bb, hb, dtype, bwd_tensor = case
+    g = torch.Generator().manual_seed(1234 + Sq + 7 * D + R)
+    q, do = (torch.randn(B, Sq, H, D, generator=g) for _ in range(2))
+    k, v = (torch.randn(B, Sk, H, D, generator=g) for _ in range(2))
+    qb = kb = None
+    if R:
+        qb = torch.randn(1 if bb else B, Sq, 1 if hb else H, R, generator=g) * 0.5
+        kb = torch.randn(1 if bb else B, Sk, 1 if hb else H, R, generator=g) * 0.5
+    host = [t.to(dtype) if t is not None else None for t in (q, k, v, qb, kb, do)]
+    dev = [t.cuda() if t is not None else None for t in host]
+    p = _lib.FbParams()
+    _fill_common(p, dev[0], dev[1], dev[2], dev[3], dev[4], None, causal, float(scale or 1.0 / math.sqrt(D)), 0)
+    o_buf = torch.empty_like(dev[0])
+    lse_buf = torch.empty(B, H, math.ceil(Sq / 128) * 128, device="cuda")
+    p.o, p.o_stride = o_buf.data_ptr(), _lib.I64x3(o_buf.stride(0), o_buf.stride(2), o_buf.stride(1))
+    p.lse, p.lse_stride_bh = lse_buf.data_ptr(), lse_buf.shape[-1]
+    assert _lib.load().fb_fwd_uses_tensor_path(C.byref(p)) == (1 if R <= 64 else 0)
+    assert _lib.load().fb_bwd_uses_tensor_path(C.byref(p)) == (1 if bwd_tensor else 0)
+
+    leaves = [t.clone().requires_grad_(True) if t is not None else None for t in dev[:5]]
+    o = flash_bias_func(leaves[0], leaves[1], leaves[2], leaves[3], leaves[4], None, causal, scale)
+    o.backward(dev[5])
+    torch.cuda.synchronize()
+    f32 = [t.float() if t is not None else None for t in host]
+    o_ref, lse_ref = orc.attention_forward(f32[0], f32[1], f32[2], f32[3], f32[4], None, causal, scale)
+    check_close("variant/o", o, o_ref, dtype)
+    g_ref = orc.attention_backward(f32[5], f32[0], f32[1], f32[2], o.detach().float().cpu(), lse_ref, f32[3], f32[4],
+                                   None, causal, scale)
+    for key, t, ref in zip(GRADS, leaves, g_ref):
+        if t is not None:
+            check_close(f"variant/{key}", t.grad, ref, dtype)
