@@ -111,7 +111,17 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int kv_end = a.causal ? min(a.Sk, q0 + 128) : a.Sk;
   const int n_kv = (kv_end + 127) / 128;
 
-  if (warp == 5) {
+  // producer thread only: the K|Kb and V tiles of key tile j
+  const int hk = a.hk_bcast ? 0 : h, bk = a.bk_bcast ? 0 : b;
+  auto load_kv = [&](int j) {
+    const int ks = j % KST, vs = j % VST;
+    mbar_expect_tx(k_full + 8 * ks, Cfg::Q_BYTES + Cfg::QB_BYTES);
+    tma_tile_4d<D>(sK + ks * Cfg::Q_BYTES, &tmK, k_full + 8 * ks, j * 128, h, b);
+    if (RP) tma_tile_4d<RPX>(sKb + ks * Cfg::QB_BYTES, &tmKb, k_full + 8 * ks, j * 128, hk, bk);
+    mbar_expect_tx(v_full + 8 * vs, Cfg::Q_BYTES);
+    tma_tile_4d<D>(sV + vs * Cfg::Q_BYTES, &tmV, v_full + 8 * vs, j * 128, h, b);
+  };
+  if (warp == 4) {
     if (lane == 0) {
       *abort_flag = 0;
       mbar_init(q_full, 1);
@@ -126,8 +136,15 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         mbar_init(v_free + 8 * i, 1);
       }
       mbar_fence_init();
+      // the first loads start before the rest of the CTA has finished its set-up
+      const int hq = a.hq_bcast ? 0 : h, bq = a.bq_bcast ? 0 : b;
+      mbar_expect_tx(q_full, NQ * Cfg::Q_BYTES + Cfg::QB_BYTES);
+#pragma unroll
+      for (int t = 0; t < NQ; ++t) tma_tile_4d<D>(sQ + t * Cfg::Q_BYTES, &tmQ, q_full, q0, h, b, t * D);
+      if (RP) tma_tile_4d<RPX>(sQb, &tmQb, q_full, q0, hq, bq);
+      for (int j = 0; j < KST && j < n_kv; ++j) load_kv(j);
     }
-    __syncwarp();
+  } else if (warp == 5) {
     tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
     tmem_relinquish();
   }
@@ -140,24 +157,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (warp == 4) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      tma_prefetch_desc(&tmQ);
-      tma_prefetch_desc(&tmK);
-      tma_prefetch_desc(&tmV);
-      const int hq = a.hq_bcast ? 0 : h, bq = a.bq_bcast ? 0 : b;
-      const int hk = a.hk_bcast ? 0 : h, bk = a.bk_bcast ? 0 : b;
-      mbar_expect_tx(q_full, NQ * Cfg::Q_BYTES + Cfg::QB_BYTES);
-#pragma unroll
-      for (int t = 0; t < NQ; ++t) tma_tile_4d<D>(sQ + t * Cfg::Q_BYTES, &tmQ, q_full, q0, h, b, t * D);
-      if (RP) tma_tile_4d<RPX>(sQb, &tmQb, q_full, q0, hq, bq);
-      for (int j = 0; j < n_kv; ++j) {
-        const int ks = j % KST, vs = j % VST;
-        if (j >= KST) mbar_wait(k_free + 8 * ks, ((j / KST) - 1) & 1, abort_flag, a.status);
-        mbar_expect_tx(k_full + 8 * ks, Cfg::Q_BYTES + Cfg::QB_BYTES);
-        tma_tile_4d<D>(sK + ks * Cfg::Q_BYTES, &tmK, k_full + 8 * ks, j * 128, h, b);
-        if (RP) tma_tile_4d<RPX>(sKb + ks * Cfg::QB_BYTES, &tmKb, k_full + 8 * ks, j * 128, hk, bk);
-        if (j >= VST) mbar_wait(v_free + 8 * vs, ((j / VST) - 1) & 1, abort_flag, a.status);
-        mbar_expect_tx(v_full + 8 * vs, Cfg::Q_BYTES);
-        tma_tile_4d<D>(sV + vs * Cfg::Q_BYTES, &tmV, v_full + 8 * vs, j * 128, h, b);
+      for (int j = KST; j < n_kv; ++j) {
+        mbar_wait(k_free + 8 * (j % KST), ((j / KST) - 1) & 1, abort_flag, a.status);
+        mbar_wait(v_free + 8 * (j % VST), ((j / VST) - 1) & 1, abort_flag, a.status);
+        load_kv(j);
       }
     }
   } else if (warp == 5) {
