@@ -330,6 +330,28 @@ def main():
         bwd_kernel_ms = kms.value / max(kn.value, 1)
         ach = fl_b / (bwd_kernel_ms * 1e-3) / 1e12 if kn.value else None
         fwd_kernel_ms = fkms.value / max(fkn.value, 1)
+        # algorithmic bytes of one backward call: reads q,k,v,o,dO,factors,lse,delta; writes dq,dk,dv,dq_bias,dk_bias
+        nfac = (w.q_bias.numel() + w.k_bias.numel()) if w.q_bias is not None else 0
+        bytes_b = 2 * (sh["B"] * sh["H"] * (4 * sh["Sq"] * sh["D"] + 4 * sh["Sk"] * sh["D"]) + 2 * nfac) + \
+            8 * sh["B"] * sh["H"] * sh["Sq"]
+        t_b = bwd_kernel_ms * 1e-3
+        tensor = {"achieved": ach, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                  "frac": (ach / peaks["bf16_tflops"]) if ach else None}
+        gbs = bytes_b / t_b / 1e9 if kn.value else None
+        hbm = {"achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+               "frac": (gbs / peaks["hbm_gbs"]) if gbs else None}
+        # the binding roofline is the one with the larger lower bound on the kernel's time
+        hbm_binds = bytes_b / (peaks["hbm_gbs"] * 1e9) > fl_b / (peaks["bf16_tflops"] * 1e12)
+        roof = {"bound": "hbm" if hbm_binds else "tensor", "kernel": "bwd_sm100_kernel",
+                **(hbm if hbm_binds else tensor), "peak_source": peaks["source"],
+                "ms_per_launch": bwd_kernel_ms, "launches_timed": kn.value, "flop_per_launch": fl_b,
+                "bytes_per_launch": bytes_b, "other_roofline": tensor if hbm_binds else hbm,
+                # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel, from the ncu capture
+                # summarised in profiles/bench_alibi_launch_list.md (full-size alibi workload)
+                "traffic": NCU_BWD_TRAFFIC_BYTES.get(args.workload)}
+        # the reference's own flop convention (benchmark.py: (4D+1) B H S^2 forward, x3 forward+backward, no
+        # causal discount), so that numbers can be laid beside its tables
+        ref_fl = 3.0 * (4 * sh["D"] + 1) * sh["B"] * sh["H"] * sh["Sq"] * sh["Sk"]
         line = {
             "metric": "fwd+bwd attention TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
@@ -340,19 +362,13 @@ def main():
                        "fwd_ms": fwd_ms, "fwd_tflops": world * fl_f / (fwd_ms * 1e-3) / 1e12,
                        "fwd_kernel_ms": fwd_kernel_ms,
                        "fwd_kernel_tflops": fl_f / (fwd_kernel_ms * 1e-3) / 1e12 if fkn.value else None,
-                       "flop_convention": "T*(14D+8R), T = attended (query,key) pairs"},
+                       "flop_convention": "T*(14D+8R), T = attended (query,key) pairs",
+                       "reference_convention_tflops": world * ref_fl / (ms_step * 1e-3) / 1e12},
             "clocks": clocks,
             "e2e": {"value": world * fl / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": int(launches),
-            "roofline": {"bound": "tensor", "kernel": "bwd_sm100_kernel", "achieved": ach,
-                         "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                         "frac": (ach / peaks["bf16_tflops"]) if ach else None, "peak_source": peaks["source"],
-                         "ms_per_launch": bwd_kernel_ms, "launches_timed": kn.value,
-                         "flop_per_launch": fl_b,
-                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel, from the ncu
-                         # capture summarised in profiles/bench_alibi_launch_list.md (full-size alibi workload)
-                         "traffic": NCU_BWD_TRAFFIC_BYTES.get(args.workload)},
+            "roofline": roof,
         }
         if not args.no_cpu_baseline and world == 1:
             from oracle import flashbias_oracle as orc
