@@ -329,11 +329,13 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       chunk_exp(rb, 1);
       tmem_wait_ld(ra);
       tmem_ld32(tSl + 96, rb);
-      chunk_exp(ra, 2);
+      // the last chunk is awaited before the arithmetic of the third: S is then entirely in registers and the
+      // tensor core starts on the next key tile half a pass earlier
       tmem_wait_ld(rb);
       tc_fence_before_sync();
       if (threadIdx.x == 0) FB_TRACE_MARK(j, 4);
-      mbar_arrive_warp(s_read);  // S is in registers: the tensor core may start on the next key tile
+      mbar_arrive_warp(s_read);
+      chunk_exp(ra, 2);
       chunk_exp(rb, 3);
       l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       tmem_wait_st();
