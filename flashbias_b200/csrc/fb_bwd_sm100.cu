@@ -631,13 +631,17 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 17);
       ds_sum1 = chunk(rs1, rd1, pk1, dk1, 1);
       if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 18);
+      // Chunk 0 of the next tile is fetched under the stores below if its S and dP are already there (they were
+      // issued when this tile was released).  If not -- a 2-stage ring delivers the next tile late -- the stores
+      // must not wait for it: they release this tile's products, which in turn free the stage.
+      bool prefetched = false;
       if (it + 1 < n_it) {
-        // chunk 0 of the next tile (its S and dP were issued when this tile was released, long done by now):
-        // the fetch runs under the stores below
-        mbar_wait(dp_full, (it + 1) & 1, abort_flag, a.status);
-        tc_fence_after_sync();
-        tmem_ld32(tSl, rs0);
-        tmem_ld32(tDl, rd0);
+        prefetched = __all_sync(0xffffffffu, mbar_test_wait(dp_full, (it + 1) & 1));
+        if (prefetched) {
+          tc_fence_after_sync();
+          tmem_ld32(tSl, rs0);
+          tmem_ld32(tDl, rd0);
+        }
       }
       // the dV, dK and dQ products of the previous query tile have read P and dS
       if (it >= 1) mbar_wait(pds_free, (it - 1) & 1, abort_flag, a.status);
@@ -661,6 +665,12 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 1);
       mbar_arrive_warp(pds_ready + 8 * (it & 1));
       if (lane == 0 && warp == 0) FB_TRACE_MARK(it, 16);
+      if (it + 1 < n_it && !prefetched) {
+        mbar_wait(dp_full, (it + 1) & 1, abort_flag, a.status);
+        tc_fence_after_sync();
+        tmem_ld32(tSl, rs0);
+        tmem_ld32(tDl, rd0);
+      }
     }
     // the dV and dK|dKb accumulators are final once every MMA of the CTA has completed
     mbar_wait(all_done, 0, abort_flag, a.status);
