@@ -75,6 +75,7 @@ struct BwdCfg {
   //   dK chain:  dS^T . [Q | Qb]   (when Qb is 32 columns wide)        dQ chain:  dS . [K | Kc]
   static constexpr bool MERGE_K = (D == 32 && RP == 32);
   static constexpr bool MERGE_Q = (D == 32 && RC == 32);
+  static constexpr bool SEP_DKB = RP && !MERGE_K;  // dKb is an accumulator (and an MMA chain) of its own
   // resident tiles of the key block: K, (hi, lo) of k*scale when the scale is not a power of two, Kb, Kc, V
   static constexpr int OFF_K = 0;
   static constexpr int OFF_KS = OFF_K + D_BYTES;
@@ -223,7 +224,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(dp_full, 1);
       mbar_init(sdp_read, 8);  // every compute warp has S and dP of the tile in registers
       mbar_init(all_done, 4);  // one commit per issuing thread
-      mbar_init(pds_free, 3);  // the dV(+dKb), dK and dQ chains have read P and dS of a query tile
+      mbar_init(pds_free, Cfg::SEP_DKB ? 4 : 3);  // the dV, dK, dQ (and dKb) chains have read P and dS of a query tile
       for (int i = 0; i < 3; ++i) {
         mbar_init(qdo_full + 8 * i, 1);
         mbar_init(qdo_free + 8 * i, 3);  // S|dP, dV and dK chains read a stage
@@ -339,6 +340,24 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const DescBase kQ = kmajor_base<D>(sStage), kDO = kmajor_base<D>(sStage + Cfg::OFF_DO),
                        kQb = kmajor_base<RPX>(sStage + Cfg::OFF_QB), kK = kmajor_base<D>(NQ == 2 ? sKs : sK),
                        kKb = kmajor_base<RPX>(sKb), kV = kmajor_base<D>(sV);
+        // dKb, when it is an accumulator of its own (no merged [Q | Qb] operand), is issued by this thread as
+        // well: between S|dP of query tile i and of tile i+1 it would otherwise idle, and the dV thread, which
+        // releases the stage of the tile, gets shorter
+        const DescBase mQbT = mnmajor_base<RPX>(sStage + Cfg::OFF_QB), mDST = mnmajor_base<128>(sDS);
+        auto issue_dKb = [&](int it) {
+          const int st = it % Cfg::NSTAGE;
+          const uint32_t so = st * Cfg::STAGE_BYTES;
+          mbar_wait(pds_ready + 8 * (it & 1), (it >> 1) & 1, abort_flag, a.status);
+          tc_fence_after_sync();
+          if (!FB_DBG(4)) {
+#pragma unroll
+            for (int s = 0; s < 8; ++s)
+              umma_ss(tmem + Cfg::T_DKB, desc_at(mDST, mnmajor_step<128>(s)), desc_at(mQbT, so + mnmajor_step<RPX>(s)),
+                      idTR, (it > 0 || s > 0) ? 1u : 0u);
+          }
+          umma_commit(qdo_free + 8 * st);  // S|dP and dKb of the tile: this thread is done with its stage
+          umma_commit(pds_free);
+        };
 #pragma unroll 1
         for (int it = 0; it < n_it; ++it) {
           const int st = it % Cfg::NSTAGE;
@@ -369,13 +388,17 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             umma_ss(tmem + Cfg::T_DP, desc_at(kDO, so + kmajor_step<D>(s)), desc_at(kV, kmajor_step<D>(s)), idS,
                     s > 0);
           umma_commit(dp_full);
-          umma_commit(qdo_free + 8 * st);
           FB_TRACE_MARK(it, 5);
+          if (Cfg::SEP_DKB) {
+            if (it > 0) issue_dKb(it - 1);
+          } else {
+            umma_commit(qdo_free + 8 * st);
+          }
         }
+        if (Cfg::SEP_DKB) issue_dKb(n_it - 1);
       } else {
         const DescBase mQ = mnmajor_base<D>(sStage), mDO = mnmajor_base<D>(sStage + Cfg::OFF_DO),
-                       mQb = mnmajor_base<RPX>(sStage + Cfg::OFF_QB), mP = mnmajor_base<128>(sP),
-                       mDS = mnmajor_base<128>(sDS);
+                       mP = mnmajor_base<128>(sP), mDS = mnmajor_base<128>(sDS);
         // [Q | Qb]: 32-column blocks of 64-byte-swizzled rows, the second block at the distance between the tiles
         const uint64_t dQQb = smem_desc(sStage, Cfg::OFF_QB, 8 * 64, 64);
         const DescBase mQQb{(uint32_t)dQQb, (uint32_t)(dQQb >> 32)};
@@ -394,12 +417,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             for (int s = 0; s < 8; ++s)  // contraction over the 128 query rows
               umma_ss(tmem + Cfg::T_DV, desc_at(mP, mnmajor_step<128>(s)), desc_at(mDO, so + mnmajor_step<D>(s)), idTD,
                       (acc0 | (s > 0)) ? 1u : 0u);
-            if (RP && !Cfg::MERGE_K) {
-#pragma unroll
-              for (int s = 0; s < 8; ++s)
-                umma_ss(tmem + Cfg::T_DKB, desc_at(mDS, mnmajor_step<128>(s)),
-                        desc_at(mQb, so + mnmajor_step<RPX>(s)), idTR, (acc0 | (s > 0)) ? 1u : 0u);
-            }
           } else {
 #pragma unroll
             for (int s = 0; s < 8; ++s) {
@@ -881,9 +898,7 @@ static int launch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t s
   void* qpack = ws + w.off_qpack;
   void* kpack = ws + w.off_kpack;
   void* kcenter = ws + w.off_kcenter;
-  if (RP) {
-    if ((rc = launch_pack(p, plan, qpack, kpack, kcenter, st))) return rc;
-  }
+  if ((rc = launch_pack_operands(p, plan, qpack, kpack, kcenter, true, ws + w.off_qs, st))) return rc;
   cudaError_t e = cudaMemsetAsync(ws + w.off_dq, 0, w.zero_bytes, st);
   if (e != cudaSuccess) return (int)e;
   CUtensorMap tQ, tK, tV, tDO, tQb, tKb, tKc, tKs;
@@ -892,7 +907,6 @@ static int launch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t s
   if (NQ == 2) {
     // key operand of S = (hi, lo) of k*scale, laid out (B, H, Sk, 2D) in the workspace
     void* ks = ws + w.off_qs;
-    if ((rc = launch_pack_kscaled(p, plan, ks, st))) return rc;
     if ((rc = make_tmap_4d(&tKs, ks, 2 * D, p->Sk, p->H, p->B, 2 * D, (int64_t)2 * D * p->Sk,
                            (int64_t)2 * D * p->Sk * p->H, D, 128)))
       return rc;

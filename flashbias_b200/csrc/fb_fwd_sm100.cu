@@ -415,14 +415,11 @@ static int launch_fwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t s
   void* qpack = ws;
   void* kpack = ws + plan.q_bytes;
   void* qs = ws + plan.q_bytes + plan.k_bytes;
-  if (RP) {
-    if ((rc = launch_pack(p, plan, qpack, kpack, nullptr, st))) return rc;
-  }
+  if ((rc = launch_pack_operands(p, plan, qpack, kpack, nullptr, false, qs, st))) return rc;
   CUtensorMap tQ, tK, tV, tQb, tKb;
   constexpr int BOXD = D > 64 ? 64 : D;
   if (NQ == 2) {
     // query operand = (hi, lo) of q*scale, laid out (B, H, Sq, 2D) in the workspace
-    if ((rc = launch_pack_qscaled(p, plan, qs, st))) return rc;
     if ((rc = make_tmap_4d(&tQ, qs, 2 * D, p->Sq, p->H, p->B, 2 * D, (int64_t)2 * D * p->Sq,
                            (int64_t)2 * D * p->Sq * p->H, BOXD, 128)))
       return rc;

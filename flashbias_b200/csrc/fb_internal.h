@@ -39,11 +39,11 @@ struct PackPlan {
 };
 // false if the rank does not fit the tensor path; for_bwd reserves room for the centred (hi, lo) k-side copy
 bool plan_pack(const fb_params* p, PackPlan* plan, bool for_bwd = false);
-// kcenter (optional, rows of plan.RC columns): k_bias minus the k_bias of the middle key of each group of 32 keys.
-int launch_pack(const fb_params* p, const PackPlan& plan, void* qpack, void* kpack, void* kcenter, cudaStream_t st);
-int launch_pack_qscaled(const fb_params* p, const PackPlan& plan, void* qs, cudaStream_t st);
-// backward: (hi, lo) of k*scale, laid out (B, H, Sk, 2D)
-int launch_pack_kscaled(const fb_params* p, const PackPlan& plan, void* ks, cudaStream_t st);
+// One launch prepares every operand of a call: packed q/k factors, kcenter (optional, rows of plan.RC columns:
+// k_bias minus the k_bias of the middle key of each group of 32 keys) and, when plan.nq == 2, the (hi, lo) split
+// of q*scale (forward) or k*scale (backward; scaled_is_key), laid out (B, H, S, 2D).
+int launch_pack_operands(const fb_params* p, const PackPlan& plan, void* qpack, void* kpack, void* kcenter,
+                         bool scaled_is_key, void* scaled, cudaStream_t st);
 
 // ---- kernels ------------------------------------------------------------------------------------
 int launch_fwd_general(const fb_params* p, cudaStream_t st);

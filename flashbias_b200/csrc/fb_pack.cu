@@ -58,14 +58,35 @@ bool plan_pack(const fb_params* p, PackPlan* plan, bool for_bwd) {
   return true;
 }
 
+// One factor: (Bx, Hx, S, R) with strides -> packed rows (and the centred copy for the k side of the backward).
+template <typename T>
+struct FactorJob {
+  const T* src;
+  int64_t sb, sh, ss;
+  int Bx, Hx, S;
+  float mult;
+  T* dst;
+  T* dst_centered;
+};
+// One tensor scaled and split: (B, H, S, D) with strides -> (B, H, S, 2D) = [hi | lo] of x * scale.
+template <typename T>
+struct ScaledJob {
+  const T* src;
+  int64_t sb, sh, ss;
+  int S;
+  T* dst;  // nullptr: no such job
+};
+
 // One thread per (b, h, s) row; the packed row is built 8 columns (one 16-byte store) at a time.
 template <typename T>
-__global__ void __launch_bounds__(256) pack_factor_kernel(const T* __restrict__ src, int64_t sb, int64_t sh, int64_t ss,
-                                                          int Bx, int Hx, int S, int R, int RP, int RC, float mult,
-                                                          T* __restrict__ dst, T* __restrict__ dst_centered,
-                                                          int* status) {
-  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // (b, h, s)
-  const int64_t total = (int64_t)Bx * Hx * S;
+__device__ __forceinline__ void pack_factor_row(const FactorJob<T>& j, int64_t idx, int R, int RP, int RC, int* status) {
+  const T* __restrict__ src = j.src;
+  const int64_t sb = j.sb, sh = j.sh, ss = j.ss;
+  const int Hx = j.Hx, S = j.S;
+  const float mult = j.mult;
+  T* __restrict__ dst = j.dst;
+  T* __restrict__ dst_centered = j.dst_centered;
+  const int64_t total = (int64_t)j.Bx * Hx * S;
   if (idx >= total) return;
   const int s = (int)(idx % S);
   const int h = (int)((idx / S) % Hx);
@@ -116,11 +137,12 @@ __global__ void __launch_bounds__(256) pack_factor_kernel(const T* __restrict__ 
 // terms.
 // One thread converts 8 consecutive elements (16-byte load, two 16-byte stores).
 template <typename T>
-__global__ void __launch_bounds__(256) pack_qscaled_kernel(const T* __restrict__ q, int64_t sb, int64_t sh, int64_t ss,
-                                                           int B, int H, int S, int D, float scale,
-                                                           T* __restrict__ qs) {
-  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // (b, h, s, d/8)
-  const int d8 = D / 8;
+__device__ __forceinline__ void pack_scaled_chunk(const ScaledJob<T>& j, int64_t idx, int B, int H, int D, float scale) {
+  const T* __restrict__ q = j.src;
+  const int64_t sb = j.sb, sh = j.sh, ss = j.ss;
+  const int S = j.S;
+  T* __restrict__ qs = j.dst;
+  const int d8 = D / 8;  // idx = (b, h, s, d/8)
   const int64_t total = (int64_t)B * H * S * d8;
   if (idx >= total) return;
   const int c = (int)(idx % d8);
@@ -143,50 +165,55 @@ __global__ void __launch_bounds__(256) pack_qscaled_kernel(const T* __restrict__
   *reinterpret_cast<uint4*>(row + D + c * 8) = lo4;
 }
 
+// All operand preparation of one call in one launch: blocks [0, nbq) pack the q-side factor, [nbq, nbq + nbk) the
+// k-side factor (and its centred copy), the rest split the scaled query (forward) or key (backward).
 template <typename T>
-static int launch_pack_t(const fb_params* p, const PackPlan& plan, void* qpack, void* kpack, void* kcenter,
-                         cudaStream_t st) {
-  const int64_t nq = (int64_t)plan.Bq * plan.Hq * p->Sq, nk = (int64_t)plan.Bk * plan.Hk * p->Sk;
-  pack_factor_kernel<T><<<(unsigned)((nq + 255) / 256), 256, 0, st>>>(
-      reinterpret_cast<const T*>(p->q_bias), p->q_bias_stride[0], p->q_bias_stride[1], p->q_bias_stride[2], plan.Bq,
-      plan.Hq, p->Sq, p->R, plan.RP, plan.RC, plan.qb_mult, reinterpret_cast<T*>(qpack), nullptr, p->status);
-  pack_factor_kernel<T><<<(unsigned)((nk + 255) / 256), 256, 0, st>>>(
-      reinterpret_cast<const T*>(p->k_bias), p->k_bias_stride[0], p->k_bias_stride[1], p->k_bias_stride[2], plan.Bk,
-      plan.Hk, p->Sk, p->R, plan.RP, plan.RC, 1.f, reinterpret_cast<T*>(kpack), reinterpret_cast<T*>(kcenter), p->status);
-  note_launch(2);
-  return (int)cudaGetLastError();
+__global__ void __launch_bounds__(256) pack_operands_kernel(FactorJob<T> fq, FactorJob<T> fk, ScaledJob<T> sc,
+                                                            unsigned nbq, unsigned nbk, int B, int H, int D, int R,
+                                                            int RP, int RC, float scale, int* status) {
+  const unsigned blk = blockIdx.x;
+  if (blk < nbq) {
+    pack_factor_row<T>(fq, (int64_t)blk * 256 + threadIdx.x, R, RP, RC, status);
+  } else if (blk < nbq + nbk) {
+    pack_factor_row<T>(fk, (int64_t)(blk - nbq) * 256 + threadIdx.x, R, RP, RC, status);
+  } else {
+    pack_scaled_chunk<T>(sc, (int64_t)(blk - nbq - nbk) * 256 + threadIdx.x, B, H, D, scale);
+  }
 }
 
-int launch_pack(const fb_params* p, const PackPlan& plan, void* qpack, void* kpack, void* kcenter, cudaStream_t st) {
-  if (plan.RP == 0) return 0;
-  return p->dtype == FB_DTYPE_F16 ? launch_pack_t<__half>(p, plan, qpack, kpack, kcenter, st)
-                                  : launch_pack_t<__nv_bfloat16>(p, plan, qpack, kpack, kcenter, st);
-}
-
-static int launch_pack_scaled(const fb_params* p, const void* src, const int64_t* stride, int S, void* dst,
-                              cudaStream_t st) {
-  const int64_t n = (int64_t)p->B * p->H * S * (p->D / 8);
-  const unsigned blocks = (unsigned)((n + 255) / 256);
-  if (p->dtype == FB_DTYPE_F16)
-    pack_qscaled_kernel<__half><<<blocks, 256, 0, st>>>(reinterpret_cast<const __half*>(src), stride[0], stride[1],
-                                                        stride[2], p->B, p->H, S, p->D, p->softmax_scale,
-                                                        reinterpret_cast<__half*>(dst));
-  else
-    pack_qscaled_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(
-        reinterpret_cast<const __nv_bfloat16*>(src), stride[0], stride[1], stride[2], p->B, p->H, S, p->D,
-        p->softmax_scale, reinterpret_cast<__nv_bfloat16*>(dst));
+template <typename T>
+static int launch_pack_operands_t(const fb_params* p, const PackPlan& plan, void* qpack, void* kpack, void* kcenter,
+                                  bool scaled_is_key, void* scaled, cudaStream_t st) {
+  FactorJob<T> fq{}, fk{};
+  ScaledJob<T> sc{};
+  unsigned nbq = 0, nbk = 0, nbs = 0;
+  if (plan.RP) {
+    fq = {reinterpret_cast<const T*>(p->q_bias), p->q_bias_stride[0], p->q_bias_stride[1], p->q_bias_stride[2],
+          plan.Bq, plan.Hq, p->Sq, plan.qb_mult, reinterpret_cast<T*>(qpack), nullptr};
+    fk = {reinterpret_cast<const T*>(p->k_bias), p->k_bias_stride[0], p->k_bias_stride[1], p->k_bias_stride[2],
+          plan.Bk, plan.Hk, p->Sk, 1.f, reinterpret_cast<T*>(kpack), reinterpret_cast<T*>(kcenter)};
+    nbq = (unsigned)(((int64_t)plan.Bq * plan.Hq * p->Sq + 255) / 256);
+    nbk = (unsigned)(((int64_t)plan.Bk * plan.Hk * p->Sk + 255) / 256);
+  }
+  if (plan.nq == 2) {
+    const int S = scaled_is_key ? p->Sk : p->Sq;
+    const int64_t* stv = scaled_is_key ? p->k_stride : p->q_stride;
+    sc = {reinterpret_cast<const T*>(scaled_is_key ? p->k : p->q), stv[0], stv[1], stv[2], S,
+          reinterpret_cast<T*>(scaled)};
+    nbs = (unsigned)(((int64_t)p->B * p->H * S * (p->D / 8) + 255) / 256);
+  }
+  if (nbq + nbk + nbs == 0) return 0;
+  pack_operands_kernel<T><<<nbq + nbk + nbs, 256, 0, st>>>(fq, fk, sc, nbq, nbk, p->B, p->H, p->D, p->R, plan.RP,
+                                                           plan.RC, p->softmax_scale, p->status);
   note_launch();
   return (int)cudaGetLastError();
 }
 
-int launch_pack_qscaled(const fb_params* p, const PackPlan& plan, void* qs, cudaStream_t st) {
-  if (plan.nq == 1) return 0;
-  return launch_pack_scaled(p, p->q, p->q_stride, p->Sq, qs, st);
-}
-
-int launch_pack_kscaled(const fb_params* p, const PackPlan& plan, void* ks, cudaStream_t st) {
-  if (plan.nq == 1) return 0;
-  return launch_pack_scaled(p, p->k, p->k_stride, p->Sk, ks, st);
+int launch_pack_operands(const fb_params* p, const PackPlan& plan, void* qpack, void* kpack, void* kcenter,
+                         bool scaled_is_key, void* scaled, cudaStream_t st) {
+  return p->dtype == FB_DTYPE_F16
+             ? launch_pack_operands_t<__half>(p, plan, qpack, kpack, kcenter, scaled_is_key, scaled, st)
+             : launch_pack_operands_t<__nv_bfloat16>(p, plan, qpack, kpack, kcenter, scaled_is_key, scaled, st);
 }
 
 }  // namespace fb
