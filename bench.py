@@ -273,40 +273,19 @@ def main():
 
     # ---- end to end: pinned host inputs -> device, fwd+bwd, results -> host, every step
     h2d = sum(t.numel() * t.element_size() for t in host)
-    out_host = None
     e2e_steps = max(3, min(args.steps, 10))
-    dq_ = [torch.empty_like(t, device=dev) for t in host]
 
-    copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+    # host tensors in, host tensors out, through the package's host entry: heads (or batch entries) are cut into
+    # chunks whose copies overlap the kernels of the neighbouring chunks; every copy is inside the timed region
+    from flashbias_b200.host_pipeline import HostPipeline
+    names = ("q", "k", "v", "q_bias", "k_bias", "do")
+    host_in = dict(zip(names, host))
+    out_like = {"o": w.q, "dq": w.q, "dk": w.k, "dv": w.v, "dq_bias": w.q_bias, "dk_bias": w.k_bias}
+    out_host = {n: torch.empty(t.shape, dtype=t.dtype).pin_memory() for n, t in out_like.items() if t is not None}
+    pipe = HostPipeline(host_in, dev)
 
     def e2e_step():
-        # inputs come in on a copy stream (dO behind the forward's operands, so it lands under the forward), o goes
-        # back to the host on a second copy stream under the backward; every copy is inside the timed region
-        nonlocal out_host
-        main = torch.cuda.current_stream()
-        copy_in.wait_stream(main)
-        with torch.cuda.stream(copy_in):
-            for dst, src in zip(dq_[:5], host[:5]):
-                dst.copy_(src, non_blocking=True)
-            ev_in = torch.cuda.Event()
-            ev_in.record()
-            dq_[5].copy_(host[5], non_blocking=True)
-            ev_do = torch.cuda.Event()
-            ev_do.record()
-        main.wait_event(ev_in)
-        qq, kk, vv, qqb, kkb = (t.detach().requires_grad_(True) for t in dq_[:5])
-        o = flash_bias_func(qq, kk, vv, qqb, kkb, None, w.causal, w.softmax_scale)
-        if out_host is None:
-            shapes = [o, qq, kk, vv, qqb, kkb]
-            out_host = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in shapes]
-        copy_out.wait_stream(main)
-        with torch.cuda.stream(copy_out):
-            out_host[0].copy_(o.detach(), non_blocking=True)
-        main.wait_event(ev_do)
-        o.backward(dq_[5])
-        for dst, src in zip(out_host[1:], (qq.grad, kk.grad, vv.grad, qqb.grad, kkb.grad)):
-            dst.copy_(src, non_blocking=True)
-        torch.cuda.synchronize()
+        pipe.run(host_in, out_host, w.causal, w.softmax_scale)
 
     e2e_step()
     barrier()
@@ -315,7 +294,7 @@ def main():
         e2e_step()
     barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-    d2h = sum(t.numel() * t.element_size() for t in out_host)
+    d2h = sum(t.numel() * t.element_size() for t in out_host.values())
 
     ms_step = ms_total / args.steps
     stats = torch.tensor([ms_step, e2e_ms, fwd_ms], device=dev, dtype=torch.float64)
