@@ -78,7 +78,11 @@ class HostPipeline:
             self.dim, n = "batch", self.B
         else:
             self.dim, n = "none", 1
-        chunks = max(1, min(chunks, n))
+        # a chunk must be worth its launches: at least ~4 MB of inputs each
+        in_bytes = sum(t.numel() * t.element_size() for t in host_in.values() if t is not None)
+        chunks = max(1, min(chunks, n, in_bytes // (4 << 20)))
+        if chunks == 1:
+            self.dim = "none"
         base, extra = divmod(n, chunks)
         self.ranges: List[Tuple[int, int]] = []
         lo = 0
