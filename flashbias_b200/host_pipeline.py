@@ -133,28 +133,37 @@ class HostPipeline:
         ready = []
         with torch.cuda.stream(self.copy_in):
             for i, (lo, hi) in enumerate(self.ranges):
-                for name in ("q", "k", "v", "q_bias", "k_bias", "do"):
-                    if host_in.get(name) is not None:
-                        self._to_device(name, host_in[name], lo, hi, i == 0)
-                ev = torch.cuda.Event()
-                ev.record()
-                ready.append(ev)
+                evs = []
+                for group in (("q", "k", "v", "q_bias", "k_bias"), ("do",)):  # dO is only needed by the backward
+                    for name in group:
+                        if host_in.get(name) is not None:
+                            self._to_device(name, host_in[name], lo, hi, i == 0)
+                    ev = torch.cuda.Event()
+                    ev.record()
+                    evs.append(ev)
+                ready.append(evs)
         keep = []  # chunk results stay referenced until their copies have completed
         d = self.dev
-        for (lo, hi), ev in zip(self.ranges, ready):
-            main.wait_event(ev)
-            q, k, v, do = (self._view(d[n], lo, hi) for n in ("q", "k", "v", "do"))
-            qb, kb = self._view(d.get("q_bias"), lo, hi), self._view(d.get("k_bias"), lo, hi)
-            o, lse, sc = flash_bias_forward(q, k, v, qb, kb, None, causal, softmax_scale)
-            dq, dk, dv, dqb, dkb = flash_bias_backward(do, q, k, v, o, qb, kb, lse, None, causal, sc)
+
+        def send_back(res, lo, hi):
             done = torch.cuda.Event()
             done.record(main)
-            res = {"o": o, "dq": dq, "dk": dk, "dv": dv, "dq_bias": dqb, "dk_bias": dkb}
-            keep.append(res)
             with torch.cuda.stream(self.copy_out):
                 self.copy_out.wait_event(done)
                 for name, t in res.items():
                     if t is not None:
                         self._to_host(host_out[name], t, lo, hi)
+
+        for (lo, hi), (ev_fwd, ev_bwd) in zip(self.ranges, ready):
+            main.wait_event(ev_fwd)
+            q, k, v, do = (self._view(d[n], lo, hi) for n in ("q", "k", "v", "do"))
+            qb, kb = self._view(d.get("q_bias"), lo, hi), self._view(d.get("k_bias"), lo, hi)
+            o, lse, sc = flash_bias_forward(q, k, v, qb, kb, None, causal, softmax_scale)
+            send_back({"o": o}, lo, hi)  # o leaves while the backward runs
+            main.wait_event(ev_bwd)
+            dq, dk, dv, dqb, dkb = flash_bias_backward(do, q, k, v, o, qb, kb, lse, None, causal, sc)
+            res = {"dq": dq, "dk": dk, "dv": dv, "dq_bias": dqb, "dk_bias": dkb}
+            send_back(res, lo, hi)
+            keep.append((o, res))
         torch.cuda.synchronize(self.device)
         return keep[-1] if keep else None
