@@ -8,10 +8,12 @@
 //               thread issues the dQ | dQb MMAs.
 //   warps 13-15 MMA issuers (one thread each, every warp on its own warp scheduler), per query tile:
 //                 13: S  = [Q|Qb].[K|Kb]^T      dP = dO.V^T                     (TMEM, fresh)
+//                     (and dKb += dS^T.Qb when it is not merged into the dK product)
 //                 14: dV += P^T.dO              15: dK|dKb += dS^T.[Q|Qb]       (TMEM, accumulated)
 //                 12: dQ|dQb = dS.[K|Kc]                                        (TMEM, fresh, two accumulators)
 //   warps 0-7   two compute warpgroups, each thread owns one query row (TMEM lane) and half of the key
-//               columns: S and dP go to registers at once (releasing them for the next tile's MMAs),
+//               columns: S and dP go to registers (fetched under the previous tile's stores, which releases
+//               them for the next tile's MMAs at the head of the tile),
 //               P = exp2(S*c - lse*log2e), dS = P*(dP - delta), both rounded to 16 bits and, once the previous
 //               tile's products have released them, written to shared memory as operand tiles.
 //   warps 8-11  drain warpgroup: the dQ|dQb tile goes from TMEM through a shared-memory staging tile into fp32
@@ -324,7 +326,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // one thread alone cannot feed the tensor core; the chains are independent (different accumulators) and
     // run concurrently:
     //   warp 13  S and dP of query tile i, as soon as tile i-1 is in registers
-    //   warp 14  dV (and dKb when it is a separate accumulator)
+    //   warp 13  also dKb when it is a separate accumulator      warp 14  dV
     //   warp 15  dK (or dK | dKb merged)
     // Every accumulator is only ever touched by one thread, which keeps its MMAs ordered.
     if (lane == 0 && n_it > 0) {
@@ -694,8 +696,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     tc_fence_after_sync();
     if (threadIdx.x == 0) FB_TRACE_MARK(0, 22);
 
-    // ---- epilogue: dV, dK (x scale), dKb (x scale, split terms folded)
-    // the last dq_full phase covered every MMA of the CTA, so the accumulators are final
+    // ---- epilogue: dV, dK (x scale), dKb
     const int krow = k0 + row;
     {
       T* dvrow = reinterpret_cast<T*>(a.dv) + b * a.dv_stride[0] + h * a.dv_stride[1] + (int64_t)krow * a.dv_stride[2];
