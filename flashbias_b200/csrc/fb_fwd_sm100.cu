@@ -2,15 +2,19 @@
 // tensor memory, warp-specialised roles.
 //
 // One CTA owns one tile of 128 query rows of one (batch, head) and walks the key/value tiles:
-//   warp 4      TMA producer: Q|packed q_bias once, then K|packed k_bias and V tiles through
-//               small rings of shared-memory stages.
-//   warp 5      MMA issuer (one thread): S = [Q|Qb].[K|Kb]^T into TMEM, then O += P.V.
+//   warp 4      TMA producer: barrier set-up and the first loads before the CTA-wide sync; Q (or the (hi, lo)
+//               split of q*scale) | packed q_bias once, then K|packed k_bias and V tiles through rings of up
+//               to four shared-memory stages.
+//   warp 5      MMA issuer (one thread): S = [Q|Qb].[K|Kb]^T into TMEM, bias products first.
+//   warp 6      MMA issuer (one thread, another warp scheduler): O += P.V with P read from TMEM.
 //   warps 0-3   softmax: one thread per query row (= one TMEM lane).  Pass 1 reads S and takes the
 //               row maximum; pass 2 reads S again, exponentiates, accumulates the row sum and writes P
-//               (16-bit, swizzled K-major operand tile) to shared memory.  O is rescaled in TMEM only
-//               when the running maximum has grown by more than 2^8 ("lazy rescale"), which is exact
-//               because the row sum carries the same reference maximum.
-// S' = q.k + (q_bias/scale).k_bias is a single accumulator; p = exp2((S' - m) * scale * log2 e).
+//               (16-bit pairs) to TMEM.  S is released as soon as its last chunk is in registers, so the
+//               next key tile's logits are computed under the remaining exponentials.  O is rescaled in
+//               TMEM only when the running maximum has grown by more than 2^8 ("lazy rescale"), which is
+//               exact because the row sum carries the same reference maximum.
+// All logit terms share one accumulator: S' = qs.k + qb.k_bias, with qs = q and qb = q_bias/scale when the
+// scale is a power of two (p = exp2((S' - m) * scale * log2 e)), else qs = (hi, lo) of q*scale and qb = q_bias.
 // Two CTAs share an SM (256 TMEM columns each) so one CTA's softmax overlaps the other's MMAs.
 #include <type_traits>
 
