@@ -25,7 +25,7 @@ import torch
 
 from .flash_bias import flash_bias_backward, flash_bias_forward
 
-__all__ = ["HostPipeline"]
+__all__ = ["HostPipeline", "plan_chunks"]
 
 _H2D, _D2H = 1, 2
 _cudart = None
@@ -60,6 +60,35 @@ def _copy_heads(dst: torch.Tensor, src: torch.Tensor, h0: int, h1: int, kind: in
         raise RuntimeError(f"cudaMemcpy2DAsync failed: {rc}")
 
 
+def plan_chunks(q_shape, q_bias_shape, k_bias_shape, in_bytes: int, chunks: int = 5):
+    """Host logic of the pipeline: along which dimension the work is cut and into which ranges.
+
+    Returns (dim, ranges) with dim in {"head", "batch", "none"}.  The dimension is one the factors are not
+    shared over, so that a factor gradient belongs to exactly one chunk; a chunk must carry at least ~4 MB of
+    inputs to be worth its launches.
+    """
+    B, _, H, _ = q_shape
+    has_bias = q_bias_shape is not None
+    per_head = (not has_bias) or (q_bias_shape[2] == H and k_bias_shape[2] == H)
+    per_batch = (not has_bias) or (q_bias_shape[0] == B and k_bias_shape[0] == B)
+    if per_head and H > 1:
+        dim, n = "head", H
+    elif per_batch and B > 1:
+        dim, n = "batch", B
+    else:
+        dim, n = "none", 1
+    chunks = max(1, min(chunks, n, in_bytes // (4 << 20)))
+    if chunks == 1:
+        return "none", [(0, n)]
+    base, extra = divmod(n, chunks)
+    ranges, lo = [], 0
+    for c in range(chunks):
+        hi = lo + base + (1 if c < extra else 0)
+        ranges.append((lo, hi))
+        lo = hi
+    return dim, ranges
+
+
 class HostPipeline:
     """Reusable device buffers and copy streams for ``run`` (one instance per problem shape)."""
 
@@ -67,29 +96,10 @@ class HostPipeline:
         q, k = host_in["q"], host_in["k"]
         self.B, self.Sq, self.H, self.D = q.shape
         self.device = torch.device(device)
-        self.has_bias = host_in.get("q_bias") is not None
         qb, kb = host_in.get("q_bias"), host_in.get("k_bias")
-        per_head = (not self.has_bias) or (qb.shape[2] == self.H and kb.shape[2] == self.H)
-        per_batch = (not self.has_bias) or (qb.shape[0] == self.B and kb.shape[0] == self.B)
-        # chunk along a dimension the factors are not shared over: a factor gradient then belongs to one chunk
-        if per_head and self.H > 1:
-            self.dim, n = "head", self.H
-        elif per_batch and self.B > 1:
-            self.dim, n = "batch", self.B
-        else:
-            self.dim, n = "none", 1
-        # a chunk must be worth its launches: at least ~4 MB of inputs each
         in_bytes = sum(t.numel() * t.element_size() for t in host_in.values() if t is not None)
-        chunks = max(1, min(chunks, n, in_bytes // (4 << 20)))
-        if chunks == 1:
-            self.dim = "none"
-        base, extra = divmod(n, chunks)
-        self.ranges: List[Tuple[int, int]] = []
-        lo = 0
-        for c in range(chunks):
-            hi = lo + base + (1 if c < extra else 0)
-            self.ranges.append((lo, hi))
-            lo = hi
+        self.dim, self.ranges = plan_chunks(tuple(q.shape), None if qb is None else tuple(qb.shape),
+                                            None if kb is None else tuple(kb.shape), in_bytes, chunks)
         self.dev = {name: torch.empty(t.shape, dtype=t.dtype, device=self.device)
                     for name, t in host_in.items() if t is not None}
         self.copy_in, self.copy_out = torch.cuda.Stream(self.device), torch.cuda.Stream(self.device)
