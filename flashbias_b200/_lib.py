@@ -38,6 +38,8 @@ class FbParams(C.Structure):
         ("dq_bias_stride", I64x3), ("dk_bias_stride", I64x3),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("status", C.c_void_p),
+        ("alibi_slopes", C.c_void_p),
+        ("mask_batch_period", C.c_int32),
     ]
 
 
@@ -54,6 +56,8 @@ EXPORTS = {
     "fb_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(FbParams)]),
     "fb_bwd_preprocess": (C.c_int, [C.POINTER(FbParams), C.c_void_p]),
     "fb_bwd": (C.c_int, [C.POINTER(FbParams), C.c_void_p]),
+    "fb_read_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_void_p]),
+    "fb_status_string": (C.c_char_p, [C.c_int32]),
     "fb_launch_count": (C.c_longlong, []),
     "fb_prof_begin": (C.c_int, [C.c_int]),
     "fb_prof_end": (C.c_int, [C.POINTER(C.c_float), C.POINTER(C.c_int)]),

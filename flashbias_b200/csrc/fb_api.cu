@@ -37,6 +37,7 @@ static int validate_common(const fb_params* p) {
   } else if (p->q_bias || p->k_bias) {
     return FB_EINVAL_BIAS;
   }
+  if (p->alibi_slopes && p->R > 0) return FB_EINVAL_BIAS;  // the producer replaces the factors
   if (p->mask_kind != FB_MASK_NONE) {
     if (p->mask_kind != FB_MASK_VECTOR && p->mask_kind != FB_MASK_MATRIX) return FB_EINVAL_MASK;
     if (!p->mask) return FB_EINVAL_MASK;
@@ -44,6 +45,7 @@ static int validate_common(const fb_params* p) {
       return FB_EINVAL_DTYPE;
     for (int i = 0; i < 3; ++i)
       if (p->mask_stride[i] < 0) return FB_EINVAL_STRIDE;
+    if (p->mask_batch_period < 0) return FB_EINVAL_MASK;
   } else if (p->mask) {
     return FB_EINVAL_MASK;
   }
@@ -147,13 +149,33 @@ extern "C" const char* fb_strerror(int code) {
     case FB_EINVAL_STRIDE: return "negative stride or non-contiguous last dimension";
     case FB_EINVAL_MASK: return "mask pointer and mask_kind disagree";
     case FB_EINVAL_WORKSPACE: return "workspace missing, misaligned or too small";
-    case FB_EINVAL_BIAS: return "q_bias and k_bias must be given together with rank > 0";
+    case FB_EINVAL_BIAS: return "q_bias and k_bias must be given together with rank > 0 (and not with alibi_slopes)";
     case FB_EINVAL_LSE: return "lse_stride_bh is smaller than Sq";
     case FB_ENOTBUILT: return "kernel variant not available in this build";
     case FB_EDEVICE: return "a kernel reported a device-side error";
     case FB_EINVAL_SIZE: return "problem needs more scratch than the fixed-capacity entry point holds";
     default: return code > 0 ? cudaGetErrorString(static_cast<cudaError_t>(code)) : "unknown flashbias error";
   }
+}
+
+extern "C" const char* fb_status_string(int32_t value) {
+  switch (value) {
+    case FB_DEV_OK: return "ok";
+    case FB_DEV_WAIT_TIMEOUT: return "a bounded wait inside a kernel expired; the results of that call are invalid";
+    case FB_DEV_FACTOR_OVERFLOW: return "a pre-scaled bias factor left the range of the 16-bit type";
+    default: return "unknown device status";
+  }
+}
+
+extern "C" int fb_read_status(const int32_t* status, int32_t* value, void* cuda_stream) {
+  if (!status) return FB_EINVAL_NULL;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
+  int32_t host = 0;
+  cudaError_t e = cudaMemcpyAsync(&host, status, sizeof(host), cudaMemcpyDefault, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return (int)e;
+  if (value) *value = host;
+  return host == FB_DEV_OK ? FB_OK : FB_EDEVICE;
 }
 
 extern "C" int fb_fwd_uses_tensor_path(const fb_params* p) {

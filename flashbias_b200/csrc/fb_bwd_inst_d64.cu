@@ -1,0 +1,23 @@
+// Backward tensor-core kernels for head_dim 64 (every packed rank that fits, both 16-bit types).
+#include "fb_bwd_sm100.cuh"
+
+namespace fb {
+
+template <typename T>
+static int dispatch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
+  if (p->alibi_slopes) return launch_bwd_t<T, 64, 0, 1, true>(p, plan, st);
+  switch (plan.RP) {
+    case 0: return launch_bwd_t<T, 64, 0, 1, false>(p, plan, st);
+    case 16: return plan.nq == 2 ? launch_bwd_t<T, 64, 16, 2, false>(p, plan, st)
+                                  : launch_bwd_t<T, 64, 16, 1, false>(p, plan, st);
+    case 32: return plan.nq == 2 ? launch_bwd_t<T, 64, 32, 2, false>(p, plan, st)
+                                  : launch_bwd_t<T, 64, 32, 1, false>(p, plan, st);
+  }
+  return FB_ENOTBUILT;
+}
+
+int dispatch_bwd_d64(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
+  return p->dtype == FB_DTYPE_F16 ? dispatch_bwd_t<__half>(p, plan, st) : dispatch_bwd_t<__nv_bfloat16>(p, plan, st);
+}
+
+}  // namespace fb

@@ -9,17 +9,12 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "flashbias_b200.h"
+
 namespace fb {
 
-// ---------------------------------------------------------------------------------------------
-// Status word written by kernels whose bounded waits expire (never a trap, never an endless spin).
-// ---------------------------------------------------------------------------------------------
-enum : int {
-  FB_DEV_OK = 0,
-  FB_DEV_WAIT_TIMEOUT = 1,   // an mbarrier wait gave up
-  FB_DEV_FACTOR_OVERFLOW = 2 // a pre-scaled bias factor left the range of the 16-bit type
-};
-
+// Kernels whose bounded waits expire store FB_DEV_WAIT_TIMEOUT (flashbias_b200.h) in the caller's status word:
+// never a trap, never an endless spin.
 constexpr uint32_t kSpinLimit = 1u << 22;  // try_wait polls before a wait gives up
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -338,6 +333,39 @@ __device__ __forceinline__ float fast_log2(float x) {
   return y;
 }
 
+// Packed fp32 pairs (sm_100 executes add/mul/fma on two fp32 values with one instruction): the softmax and
+// P/dS loops are bound by instruction issue, not by the FMA pipe, so halving their FMA-pipe instructions pays.
+__device__ __forceinline__ uint64_t f2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
+// max of three values in one instruction (sm_100)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 template <typename T> struct Pack2;
 template <> struct Pack2<__half> {
   static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
@@ -360,6 +388,26 @@ template <typename T> __device__ __forceinline__ T from_f32(float x);
 template <> __device__ __forceinline__ __half from_f32<__half>(float x) { return __float2half_rn(x); }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
 template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
+
+// 32 consecutive mask values of one row as fp32 (times log2 e).  `p` points at the first of them; `n` of them
+// exist (the rest read as 0); `vec` says that p is 16-byte aligned and n == 32.
+template <typename MT>
+__device__ __forceinline__ void load_mask_chunk(const MT* __restrict__ p, int n, bool vec, float (&mv)[32]) {
+  constexpr float kLog2e = 1.4426950408889634f;
+  if (vec) {
+    constexpr int PER = 16 / (int)sizeof(MT);
+#pragma unroll
+    for (int g = 0; g < 32 / PER; ++g) {
+      const uint4 w = __ldg(reinterpret_cast<const uint4*>(p) + g);
+      const MT* e = reinterpret_cast<const MT*>(&w);
+#pragma unroll
+      for (int i = 0; i < PER; ++i) mv[g * PER + i] = to_f32(e[i]) * kLog2e;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) mv[i] = i < n ? to_f32(p[i]) * kLog2e : 0.f;
+  }
+}
 
 // Byte offset of the 16-byte chunk holding columns [col, col+8) of `row` inside a [128][C] tile
 // (the layout described above); `col` is a multiple of 8.

@@ -24,6 +24,7 @@ __device__ __forceinline__ float warp_sum(float x) {
 
 __device__ __forceinline__ float load_mask(const fb_params& p, int b, int h, int row, int col) {
   if (p.mask_kind == FB_MASK_NONE) return 0.f;
+  if (p.mask_batch_period > 0) b %= p.mask_batch_period;
   const int64_t off = b * p.mask_stride[0] + h * p.mask_stride[1] +
                       (p.mask_kind == FB_MASK_MATRIX ? row * p.mask_stride[2] : 0) + col;
   if (p.mask_dtype == FB_DTYPE_F32) return reinterpret_cast<const float*>(p.mask)[off];
@@ -50,6 +51,7 @@ __device__ __forceinline__ float logit(const fb_params& p, const float* sq, cons
     for (int r = 0; r < p.R; ++r) bb += sqb[r] * to_f32(kb[r]);
     acc += bb;
   }
+  if (p.alibi_slopes) acc += p.alibi_slopes[h] * (float)(j - i);
   return acc + load_mask(p, b, h, i, j);
 }
 
@@ -272,6 +274,7 @@ __global__ void __launch_bounds__(kWarps * 32) bwd_dkv_general_kernel(const fb_p
           for (int r = 0; r < p.R; ++r) bb += to_f32(qb[r]) * s_kb[warp][r];
           s += bb;
         }
+        if (p.alibi_slopes) s += p.alibi_slopes[h] * (float)(j - i);
         s += load_mask(p, b, h, i, j);
         pj = __expf(s - lse);
         ds = pj * (dp - p.delta[(int64_t)bh * p.lse_stride_bh + i]);

@@ -9,7 +9,7 @@
 //     terms as large as an ALiBi position cancel inside one MMA instead of being rounded first.
 // The backward keeps its key tile resident and streams the query tiles, so it puts the split on the key side
 // instead: S = q.(k*scale), with k*scale as a (hi, lo) pair.
-// Factors are zero-padded to RP columns (16/32/64).  The backward also gets a centred k-side copy
+// Factors are zero-padded to RP columns (16/32/64; the forward also takes 128).  The backward also gets a centred k-side copy
 // (k_bias minus the k_bias of the middle key of its group of 32 keys, as a (hi, lo) pair).
 #include <math.h>
 
@@ -30,9 +30,13 @@ bool plan_pack(const fb_params* p, PackPlan* plan, bool for_bwd) {
   plan->Bk = p->k_bias_stride[0] == 0 ? 1 : p->B;
   plan->Hk = p->k_bias_stride[1] == 0 ? 1 : p->H;
   int e;
-  const bool pow2 = frexpf(p->softmax_scale, &e) == 0.5f;
+  bool pow2 = frexpf(p->softmax_scale, &e) == 0.5f;
+  // fp16 factors divided by a scale below one could leave the range of the type: take the split form instead
+  if (pow2 && p->dtype == FB_DTYPE_F16 && p->softmax_scale != 1.f && p->R > 0) pow2 = false;
+  // without factor operands nothing shares the accumulator with q.k: the scale lives in the exponent multiplier
+  if (p->R <= 0) pow2 = true;
   plan->nq = pow2 ? 1 : 2;
-  plan->qb_mult = pow2 ? (float)(1.0 / (double)p->softmax_scale) : 1.f;
+  plan->qb_mult = (pow2 && p->R > 0) ? (float)(1.0 / (double)p->softmax_scale) : 1.f;
   // forward: scaled-query copy; backward: scaled-key copy
   plan->qs_bytes = pow2 ? 0 : round256((size_t)p->B * p->H * (for_bwd ? p->Sk : p->Sq) * 2 * p->D * 2);
   plan->RC = 0;
@@ -47,7 +51,7 @@ bool plan_pack(const fb_params* p, PackPlan* plan, bool for_bwd) {
   // backward at head_dim 32: factor tiles as wide as the Q/K tiles, so that [Q | Qb] and [K | Kc] are read as one
   // MMA operand each (one product instead of two per 16 query rows / keys)
   if (for_bwd && p->D == 32 && plan->RP < 32) plan->RP = 32;
-  if (plan->RP > 64) return false;
+  if (plan->RP > (for_bwd ? 64 : 128)) return false;
   plan->q_bytes = round256((size_t)plan->Bq * plan->Hq * p->Sq * plan->RP * 2);
   plan->k_bytes = round256((size_t)plan->Bk * plan->Hk * p->Sk * plan->RP * 2);
   if (for_bwd) {

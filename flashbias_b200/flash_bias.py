@@ -20,7 +20,8 @@ import torch
 
 from . import _lib
 
-__all__ = ["FlashBiasFunc", "flash_bias_func", "flash_bias_forward", "flash_bias_backward"]
+__all__ = ["FlashBiasFunc", "flash_bias_func", "flash_bias_forward", "flash_bias_backward",
+           "FlashBiasAlibiFunc", "flash_bias_alibi_func", "check_device_status"]
 
 _DT = {torch.float16: _lib.FB_DTYPE_F16, torch.bfloat16: _lib.FB_DTYPE_BF16, torch.float32: _lib.FB_DTYPE_F32}
 
@@ -35,7 +36,35 @@ def _factor_strides(t: torch.Tensor):
     return _lib.I64x3(0 if t.shape[0] == 1 else t.stride(0), 0 if t.shape[2] == 1 else t.stride(2), t.stride(1))
 
 
-def _fill_common(p: _lib.FbParams, q, k, v, q_bias, k_bias, mask, causal, softmax_scale, flags):
+_status = None
+
+
+def _status_word() -> torch.Tensor:
+    """One int32 in pinned (device-visible) host memory: kernels store a device-side error code there, the host
+    reads it without synchronising anything."""
+    global _status
+    if _status is None:
+        _status = torch.zeros(1, dtype=torch.int32).pin_memory()
+    return _status
+
+
+def check_device_status() -> None:
+    """Raise if a kernel of an earlier call reported a device-side error (a bounded wait that expired, a factor
+    that overflowed the 16-bit type); the results of that call are invalid.  Called at the start of every
+    forward and backward; callers can also call it after a synchronisation point of their own."""
+    if _status is None:
+        return
+    code = int(_status[0])
+    if code != 0:
+        _status.zero_()
+        raise RuntimeError(f"flashbias_b200: device-side error {code}: "
+                           f"{_lib.load().fb_status_string(code).decode()} [{_lib.strerror(-10)}]")
+
+
+_ws_cache = {}
+
+
+def _fill_common(p: _lib.FbParams, q, k, v, q_bias, k_bias, mask, causal, softmax_scale, flags, alibi_slopes=None):
     batch, seqlen_q, nheads, d = q.shape
     _, seqlen_k, _, _ = k.shape
     p.B, p.H, p.Sq, p.Sk, p.D = batch, nheads, seqlen_q, seqlen_k, d
@@ -44,6 +73,9 @@ def _fill_common(p: _lib.FbParams, q, k, v, q_bias, k_bias, mask, causal, softma
     p.causal = 1 if causal else 0
     p.flags = flags
     p.softmax_scale = softmax_scale
+    p.status = _status_word().data_ptr()
+    if alibi_slopes is not None:
+        p.alibi_slopes = alibi_slopes.data_ptr()
     p.q, p.k, p.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
     p.q_stride, p.k_stride, p.v_stride = _strides_bhs(q), _strides_bhs(k), _strides_bhs(v)
     if q_bias is not None:
@@ -57,6 +89,8 @@ def _fill_common(p: _lib.FbParams, q, k, v, q_bias, k_bias, mask, causal, softma
         p.mask_stride = _lib.I64x3(0 if mask.shape[0] == 1 else mask.stride(0),
                                    0 if mask.shape[1] == 1 else mask.stride(1),
                                    0 if mask.shape[2] == 1 else mask.stride(2))
+        # a mask with fewer batch entries than q is read periodically (entry b % n): Swin's shift mask
+        p.mask_batch_period = mask.shape[0] if 1 < mask.shape[0] < batch else 0
 
 
 def _check_inputs(q, k, v, q_bias, k_bias, mask):
@@ -83,19 +117,32 @@ def _check_inputs(q, k, v, q_bias, k_bias, mask):
         assert mask.dim() == 4
         if mask.shape[2:] != (1, seqlen_k) and mask.shape[2:] != (seqlen_q, seqlen_k):
             raise RuntimeError("Last 2 dimensions of mask must be (1, seqlen_k) or (seqlen_q, seqlen_k)")
-        assert mask.shape[0] in (1, batch) and mask.shape[1] in (1, nheads)
+        # the reference expands the mask over batch and heads (:1128); a mask of n batch entries with n
+        # dividing the batch is also taken and read periodically, which is what Swin's repeat() produces
+        assert (mask.shape[0] in (1, batch) or batch % mask.shape[0] == 0) and mask.shape[1] in (1, nheads)
 
 
 def _workspace(nbytes: int, device) -> Optional[torch.Tensor]:
-    return torch.empty(nbytes, dtype=torch.uint8, device=device) if nbytes else None
+    """Scratch for one call.  One buffer per (device, stream) is kept and grown on demand: calls on a stream
+    are ordered, so the next call may overwrite it, and no allocation happens in the steady state."""
+    if not nbytes:
+        return None
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _ws_cache.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _ws_cache[key] = ws
+    return ws
 
 
-def flash_bias_forward(q, k, v, q_bias=None, k_bias=None, mask=None, causal=False, softmax_scale=None, flags=0):
+def flash_bias_forward(q, k, v, q_bias=None, k_bias=None, mask=None, causal=False, softmax_scale=None, flags=0,
+                       alibi_slopes=None):
     """Forward launch (the role of ``_flash_attn_forward``, flash_bias_triton.py:1100-1194).
 
     Returns (o, lse, softmax_scale); lse is fp32 of shape (B, H, ceil(Sq/128)*128).
     """
     lib = _lib.load()
+    check_device_status()
     _check_inputs(q, k, v, q_bias, k_bias, mask)
     batch, seqlen_q, nheads, d = q.shape
     softmax_scale = softmax_scale or 1.0 / math.sqrt(d)
@@ -105,7 +152,7 @@ def flash_bias_forward(q, k, v, q_bias=None, k_bias=None, mask=None, causal=Fals
     lse = torch.empty((batch, nheads, seqlen_q_rounded), device=q.device, dtype=torch.float32)
     o = torch.empty_like(q)
     p = _lib.FbParams()
-    _fill_common(p, q, k, v, q_bias, k_bias, mask, causal, float(softmax_scale), flags)
+    _fill_common(p, q, k, v, q_bias, k_bias, mask, causal, float(softmax_scale), flags, alibi_slopes)
     p.o, p.o_stride = o.data_ptr(), _strides_bhs(o)
     p.lse, p.lse_stride_bh = lse.data_ptr(), seqlen_q_rounded
     with torch.cuda.device(q.device):
@@ -116,12 +163,14 @@ def flash_bias_forward(q, k, v, q_bias=None, k_bias=None, mask=None, causal=Fals
     return o, lse, softmax_scale
 
 
-def flash_bias_backward(do, q, k, v, o, q_bias, k_bias, lse, mask=None, causal=False, softmax_scale=None, flags=0):
+def flash_bias_backward(do, q, k, v, o, q_bias, k_bias, lse, mask=None, causal=False, softmax_scale=None, flags=0,
+                        alibi_slopes=None):
     """Backward launches (the role of ``_flash_attn_backward``, flash_bias_triton.py:1197-1342).
 
     Returns (dq, dk, dv, dq_bias, dk_bias); factor gradients have the shape of the factors.
     """
     lib = _lib.load()
+    check_device_status()
     if do.stride(-1) != 1:
         do = do.contiguous()
     batch, seqlen_q, nheads, d = q.shape
@@ -135,7 +184,7 @@ def flash_bias_backward(do, q, k, v, o, q_bias, k_bias, lse, mask=None, causal=F
     dk_bias = torch.empty_like(k_bias) if k_bias is not None else None
     delta = torch.empty_like(lse)
     p = _lib.FbParams()
-    _fill_common(p, q, k, v, q_bias, k_bias, mask, causal, float(softmax_scale), flags)
+    _fill_common(p, q, k, v, q_bias, k_bias, mask, causal, float(softmax_scale), flags, alibi_slopes)
     p.o, p.o_stride = o.data_ptr(), _strides_bhs(o)
     p.lse, p.lse_stride_bh = lse.data_ptr(), seqlen_q_rounded
     p.dout, p.dout_stride = do.data_ptr(), _strides_bhs(do)
@@ -155,6 +204,31 @@ def flash_bias_backward(do, q, k, v, o, q_bias, k_bias, lse, mask=None, causal=F
     return dq, dk, dv, dq_bias, dk_bias
 
 
+def _narrow_expanded(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    """A factor passed as an expanded view (size > 1, stride 0 on batch or heads) is a broadcast factor: hand the
+    library the size-1 view, so that its gradient is the fp32 sum over the broadcast dimension."""
+    if t is None:
+        return None
+    for dim in (0, 2):
+        if t.shape[dim] > 1 and t.stride(dim) == 0:
+            t = t.narrow(dim, 0, 1)
+    return t
+
+
+def _widen_grad(g: Optional[torch.Tensor], shape) -> Optional[torch.Tensor]:
+    """Gradient for an input that was an expanded view: autograd sums the gradient over the expanded
+    dimension, so the summed gradient goes into entry 0 and the other entries are zero."""
+    if g is None or tuple(g.shape) == tuple(shape):
+        return g
+    full = torch.zeros(shape, dtype=g.dtype, device=g.device)
+    view = full
+    for dim in (0, 2):
+        if g.shape[dim] != shape[dim]:
+            view = view.narrow(dim, 0, 1)
+    view.copy_(g)
+    return full
+
+
 class FlashBiasFunc(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, q_bias=None, k_bias=None, mask=None, causal=False, softmax_scale=None):
@@ -171,6 +245,9 @@ class FlashBiasFunc(torch.autograd.Function):
             q, k, v, q_bias, k_bias = [x if x.stride(-1) == 1 else x.contiguous() for x in [q, k, v, q_bias, k_bias]]
         else:
             q, k, v = [x if x.stride(-1) == 1 else x.contiguous() for x in [q, k, v]]
+        ctx.factor_shapes = (None if q_bias is None else tuple(q_bias.shape),
+                             None if k_bias is None else tuple(k_bias.shape))
+        q_bias, k_bias = _narrow_expanded(q_bias), _narrow_expanded(k_bias)
         o, lse, ctx.softmax_scale = flash_bias_forward(
             q, k, v, q_bias, k_bias, mask=mask, causal=causal, softmax_scale=softmax_scale)
         ctx.save_for_backward(q, k, v, o, q_bias, k_bias, lse, mask)
@@ -184,7 +261,42 @@ class FlashBiasFunc(torch.autograd.Function):
         with torch.inference_mode():
             dq, dk, dv, dq_bias, dk_bias = flash_bias_backward(
                 do, q, k, v, o, q_bias, k_bias, lse, mask=mask, causal=ctx.causal, softmax_scale=ctx.softmax_scale)
+            dq_bias = _widen_grad(dq_bias, ctx.factor_shapes[0])
+            dk_bias = _widen_grad(dk_bias, ctx.factor_shapes[1])
         return dq, dk, dv, dq_bias, dk_bias, None, None, None
 
 
 flash_bias_func = FlashBiasFunc.apply
+
+
+class FlashBiasAlibiFunc(torch.autograd.Function):
+    """Attention with the ALiBi bias ``slopes[h] * (j - i)`` generated inside the kernels.
+
+    The reference's language-model call site builds this bias as rank-2 factors from the positions and the
+    per-head slopes (1_Language_Model/attention_with_alibi_bias.py:47-52) and feeds them to
+    ``flash_bias_func``; here the slopes go in directly, the positions never exist as tensors and are never
+    rounded to 16 bits.  ``slopes`` is an fp32 tensor of ``nheads`` values, a constant (the reference
+    registers it as a buffer): it gets no gradient.
+    """
+
+    @staticmethod
+    def forward(ctx, q, k, v, slopes, causal=True, softmax_scale=None):
+        q, k, v = [x if x.stride(-1) == 1 else x.contiguous() for x in [q, k, v]]
+        slopes = slopes.detach().to(device=q.device, dtype=torch.float32).reshape(-1).contiguous()
+        assert slopes.numel() == q.shape[2], "one slope per head"
+        o, lse, ctx.softmax_scale = flash_bias_forward(q, k, v, causal=causal, softmax_scale=softmax_scale,
+                                                       alibi_slopes=slopes)
+        ctx.save_for_backward(q, k, v, o, lse, slopes)
+        ctx.causal = causal
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse, slopes = ctx.saved_tensors
+        with torch.inference_mode():
+            dq, dk, dv, _, _ = flash_bias_backward(do, q, k, v, o, None, None, lse, causal=ctx.causal,
+                                                   softmax_scale=ctx.softmax_scale, alibi_slopes=slopes)
+        return dq, dk, dv, None, None, None
+
+
+flash_bias_alibi_func = FlashBiasAlibiFunc.apply

@@ -24,7 +24,7 @@
 extern "C" {
 #endif
 
-#define FB_VERSION 1
+#define FB_VERSION 2
 
 /* element types */
 #define FB_DTYPE_F16 0
@@ -90,8 +90,31 @@ typedef struct fb_params {
 
   void *workspace; /* scratch of at least fb_{fwd,bwd}_workspace_bytes(); 256-byte aligned */
   size_t workspace_bytes;
-  int32_t *status; /* optional device int32, zeroed by the caller; kernels store a non-zero code on a device-side error */
+  int32_t *status; /* optional int32 the device can write (device memory or mapped pinned host memory), zeroed by
+                      the caller; kernels store a non-zero FB_DEV_* code there on a device-side error */
+
+  /*
+   * Fused bias producer (optional).  alibi_slopes: fp32, one slope per head (H values).  When given, the bias
+   * slope[h] * (col - row) is generated inside the kernels from the row and column indices instead of being read
+   * as factors: it is the bias of the rank-2 factors q_bias[i] = [-m i, 1], k_bias[j] = [1, m j]
+   * (1_Language_Model/attention_with_alibi_bias.py:8-15, 47-52) evaluated in fp32, without the rounding of the
+   * positions to 16 bits.  q_bias / k_bias must then be null and R = 0; the slopes are constants (the reference
+   * registers them as a buffer), so the backward returns dq, dk, dv only.
+   */
+  const float *alibi_slopes;
+
+  /*
+   * mask_batch_period > 0: the mask holds that many batch entries and batch entry b reads entry b % period.
+   * Swin-V2 repeats its (nW, N, N) shift mask B/nW times along the batch (2_Vision_Transformer/
+   * swin_transformer_v2.py:189-192); with the period the nW masks are read in place and stay in L2.
+   */
+  int32_t mask_batch_period;
 } fb_params;
+
+/* values of *status */
+#define FB_DEV_OK 0
+#define FB_DEV_WAIT_TIMEOUT 1    /* a bounded wait inside a kernel expired; the results of that call are invalid */
+#define FB_DEV_FACTOR_OVERFLOW 2 /* a pre-scaled bias factor left the range of the 16-bit type */
 
 int fb_version(void);
 size_t fb_params_size(void); /* sizeof(fb_params) as compiled, for bindings to check their mirror of the struct */
@@ -109,6 +132,15 @@ int fb_bwd_preprocess(const fb_params *p, void *cuda_stream);
 int fb_bwd(const fb_params *p, void *cuda_stream);
 
 /*
+ * Reads a status word after the work queued on `cuda_stream` has completed (copies it to the host and
+ * synchronises that stream): FB_OK if it is zero, FB_EDEVICE otherwise; *value (optional) receives the word.
+ * No counterpart in the reference, whose kernels have no device-side error path.  A caller that keeps the
+ * word in mapped pinned host memory can simply read it instead.
+ */
+int fb_read_status(const int32_t *status, int32_t *value, void *cuda_stream);
+const char *fb_status_string(int32_t value);
+
+/*
  * fb_fwd for callers that cannot allocate device memory.  This entry point has no counterpart in the
  * reference, whose launcher allocates its scratch with torch.
  *
@@ -124,7 +156,9 @@ int fb_bwd(const fb_params *p, void *cuda_stream);
  * cudaFree or other allocating call is made.
  *
  * The first call on each device looks up the device address of the array (cudaGetSymbolAddress, with
- * that device current); make that first call outside any stream capture.  All calls on a device share
+ * that device current), and the first call of each kernel variant on a device raises that kernel's
+ * shared-memory limit (and, under lazy module loading, loads its code); make one warm-up call per device
+ * and problem kind outside any stream capture and outside the hook that forbids allocation.  All calls on a device share
  * the one array, which keeps the previous call's contents: every byte a call reads it has written
  * itself first, so nothing needs clearing, but two calls that overlap on the GPU (different streams)
  * race on it -- keep them on one stream or order them with events.

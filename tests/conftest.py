@@ -24,3 +24,14 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_sessionfinish(session, exitstatus):
+    """Write the achieved parity errors of this session where FB_PARITY_REPORT points (optional)."""
+    path = os.environ.get("FB_PARITY_REPORT")
+    if not path:
+        return
+    import json
+    from tests import helpers
+    with open(path, "w") as f:
+        json.dump(helpers.ACHIEVED, f, indent=1, sort_keys=True)

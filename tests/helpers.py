@@ -15,6 +15,11 @@ MAX_ABS_TOL = 2e-2
 REL_L2_TOL = 1e-3
 
 
+# Achieved errors of every check_close call of the session, keyed by the check's name: dumped as JSON to the path
+# in the environment variable FB_PARITY_REPORT (if set) when the session ends (tests/conftest.py).
+ACHIEVED = {}
+
+
 def golden_names():
     return sorted(os.path.splitext(os.path.basename(p))[0] for p in glob.glob(os.path.join(GOLDEN_DIR, "*.npz")))
 
@@ -55,6 +60,8 @@ def check_close(name, got, want_fp32, out_dtype, max_abs_tol=MAX_ABS_TOL, rel_l2
     tol = max_abs_tol * max(1.0, mag)
     ma = max_abs(got, want)
     rl = rel_l2(got, want.to(out_dtype).float())
+    ACHIEVED[name] = {"max_abs": ma, "rel_l2_vs_rounded": rl, "rel_l2_vs_fp32": rel_l2(got, want), "want_max": mag,
+                      "dtype": str(out_dtype).replace("torch.", "")}
     assert ma <= tol, f"{name}: max-abs {ma:.3e} > {tol:.3e} (|want|max {mag:.3e}, rel-l2 {rl:.3e})"
     gate = rel_l2_tol * (4.0 if out_dtype == torch.bfloat16 else 1.0)
     assert rl <= gate, f"{name}: rel-l2 {rl:.3e} > {gate:.1e} (max-abs {ma:.3e})"

@@ -118,10 +118,15 @@ VARIANTS = [
     (1, 2, 256, 256, 32, 24, False, None, True, True, torch.bfloat16, True),    # packed rank 64
     (1, 2, 130, 400, 32, 4, True, None, False, False, torch.bfloat16, True),    # causal Sq < Sk: key tiles no query sees
     (1, 2, 384, 384, 64, 0, True, None, False, False, torch.bfloat16, True),
-    (2, 2, 256, 256, 64, 12, False, None, False, True, torch.float16, True),    # head_dim 64, packed rank 32
+    (2, 2, 256, 256, 64, 12, False, None, False, True, torch.bfloat16, True),   # head_dim 64, packed rank 32
+    (2, 2, 256, 256, 64, 12, False, None, False, True, torch.float16, False),   # fp16 + power-of-two scale: split form,
+                                                                                 # which does not fit the backward here
     (1, 2, 200, 456, 64, 5, False, 0.1, True, False, torch.bfloat16, True),     # scale not a power of two
     (1, 2, 256, 256, 128, 8, False, None, False, False, torch.bfloat16, False),  # backward: shape-generic
     (1, 2, 256, 256, 32, 40, False, None, False, False, torch.bfloat16, False),  # rank too large for the backward
+    (1, 2, 256, 256, 128, 40, False, None, False, False, torch.bfloat16, False),  # head_dim 128, packed rank 64, split scale
+    (1, 2, 256, 256, 64, 40, False, 0.125, False, False, torch.float16, False),   # head_dim 64, packed rank 64
+    (1, 2, 200, 200, 64, 70, False, None, False, False, torch.bfloat16, False),   # packed rank 128
 ]
 
 
@@ -146,7 +151,7 @@ def test_tensor_kernel_variants(case):
     lse_buf = torch.empty(B, H, math.ceil(Sq / 128) * 128, device="cuda")
     p.o, p.o_stride = o_buf.data_ptr(), _lib.I64x3(o_buf.stride(0), o_buf.stride(2), o_buf.stride(1))
     p.lse, p.lse_stride_bh = lse_buf.data_ptr(), lse_buf.shape[-1]
-    assert _lib.load().fb_fwd_uses_tensor_path(C.byref(p)) == (1 if R <= 64 else 0)
+    assert _lib.load().fb_fwd_uses_tensor_path(C.byref(p)) == (1 if R <= 128 else 0)
     assert _lib.load().fb_bwd_uses_tensor_path(C.byref(p)) == (1 if bwd_tensor else 0)
 
     leaves = [t.clone().requires_grad_(True) if t is not None else None for t in dev[:5]]

@@ -39,6 +39,14 @@ def test_noalloc_forward_matches_regular_forward_twice():
         rc = lib.fb_fwd_noalloc(C.byref(p), stream)
         assert rc == 0, _lib.strerror(rc)
         torch.cuda.synchronize()
+        # a second call of the same problem (the kernel variant and the scratch address are set up by now)
+        # must leave the amount of free device memory untouched: nothing is allocated inside the call
+        free0, _ = torch.cuda.mem_get_info()
+        rc = lib.fb_fwd_noalloc(C.byref(p), stream)
+        assert rc == 0, _lib.strerror(rc)
+        torch.cuda.synchronize()
+        free1, _ = torch.cuda.mem_get_info()
+        assert free1 == free0, "fb_fwd_noalloc changed the free device memory"
         Sq = w.q.shape[1]
         assert (o.float() - o_ref.float()).abs().max().item() <= 2e-2
         assert (lse[..., :Sq] - lse_ref[..., :Sq]).abs().max().item() <= 2e-2
