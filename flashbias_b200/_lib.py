@@ -58,6 +58,9 @@ EXPORTS = {
     "fb_bwd": (C.c_int, [C.POINTER(FbParams), C.c_void_p]),
     "fb_read_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_void_p]),
     "fb_status_string": (C.c_char_p, [C.c_int32]),
+    "fb_prepare_rows": (C.c_int, [C.c_void_p, C.c_int32, C.POINTER(C.c_int64), C.c_void_p, C.c_int32,
+                                  C.POINTER(C.c_int64), C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                  C.c_void_p, C.c_float, C.c_void_p]),
     "fb_launch_count": (C.c_longlong, []),
     "fb_prof_begin": (C.c_int, [C.c_int]),
     "fb_prof_end": (C.c_int, [C.POINTER(C.c_float), C.POINTER(C.c_int)]),

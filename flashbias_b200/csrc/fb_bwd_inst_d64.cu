@@ -3,17 +3,23 @@
 
 namespace fb {
 
-template <typename T>
-static int dispatch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
-  if (p->alibi_slopes) return launch_bwd_t<T, 64, 0, 1, true>(p, plan, st);
+template <typename T, int MODE>
+static int dispatch_rank(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
   switch (plan.RP) {
-    case 0: return launch_bwd_t<T, 64, 0, 1, false>(p, plan, st);
-    case 16: return plan.nq == 2 ? launch_bwd_t<T, 64, 16, 2, false>(p, plan, st)
-                                  : launch_bwd_t<T, 64, 16, 1, false>(p, plan, st);
-    case 32: return plan.nq == 2 ? launch_bwd_t<T, 64, 32, 2, false>(p, plan, st)
-                                  : launch_bwd_t<T, 64, 32, 1, false>(p, plan, st);
+    case 0: return launch_bwd_t<T, 64, 0, 1, MODE>(p, plan, st);
+    case 16: return plan.nq == 2 ? launch_bwd_t<T, 64, 16, 2, MODE>(p, plan, st)
+                                  : launch_bwd_t<T, 64, 16, 1, MODE>(p, plan, st);
+    case 32: return plan.nq == 2 ? launch_bwd_t<T, 64, 32, 2, MODE>(p, plan, st)
+                                  : launch_bwd_t<T, 64, 32, 1, MODE>(p, plan, st);
   }
   return FB_ENOTBUILT;
+}
+
+template <typename T>
+static int dispatch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
+  if (p->alibi_slopes) return launch_bwd_t<T, 64, 0, 1, BWD_ALIBI>(p, plan, st);
+  if (p->mask_kind != FB_MASK_NONE) return dispatch_rank<T, BWD_MASK>(p, plan, st);
+  return dispatch_rank<T, BWD_PLAIN>(p, plan, st);
 }
 
 int dispatch_bwd_d64(const fb_params* p, const PackPlan& plan, cudaStream_t st) {

@@ -159,7 +159,10 @@ __host__ __device__ __forceinline__ int dq_stage_off(int r, int ch) {
 
 enum { BWD_PLAIN = 0, BWD_MASK = 1, BWD_ALIBI = 2 };
 
-template <typename T, int D, int RP, int NQ, bool ALIBI>
+// MODE: how the logits are completed -- as computed (BWD_PLAIN), plus an additive mask tensor (BWD_MASK), plus the
+// fused ALiBi term (BWD_ALIBI).  A kernel parameter rather than a run-time branch: the mask path needs 32 more
+// registers per thread in the P/dS loop, which would otherwise spill in every variant.
+template <typename T, int D, int RP, int NQ, int MODE>
 __global__ void __launch_bounds__(512, 1)
 bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
@@ -566,10 +569,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     float lse_raw, dlt;
     load_row_stats(0, lse_raw, dlt);
     float slope2 = 0.f;  // ALiBi slope of this head, times log2 e
-    if (ALIBI) slope2 = __ldg(a.alibi_slopes + h) * kLog2e;
+    if (MODE == BWD_ALIBI) slope2 = __ldg(a.alibi_slopes + h) * kLog2e;
     const char* mrow = nullptr;  // additive mask of this (batch, head), row 0
     int msize = 4;
-    if (!ALIBI && a.mask_kind != FB_MASK_NONE) {
+    if (MODE == BWD_MASK) {
       msize = a.mask_dtype == FB_DTYPE_F32 ? 4 : 2;
       const int mb = a.mask_batch_period > 0 ? b % a.mask_batch_period : b;
       mrow = reinterpret_cast<const char*>(a.mask) + (mb * a.mask_stride[0] + h * a.mask_stride[1]) * msize;
@@ -602,9 +605,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       // P and dS of the tile stay in registers as packed 16-bit pairs (16 words per 32-column chunk each) until
       // both chunks are done: the shared-memory tiles are still being read by the products of the previous tile.
       // MODE: how the logits are completed (plain / + mask tensor / + ALiBi term).
-      auto chunk = [&](uint32_t (&rs)[32], uint32_t (&rd)[32], uint32_t (&pk)[16], uint32_t (&dk)[16], int c,
-                       auto mode_c) {
-        constexpr int MODE = decltype(mode_c)::value;
+      auto chunk = [&](uint32_t (&rs)[32], uint32_t (&rd)[32], uint32_t (&pk)[16], uint32_t (&dk)[16], int c) {
         const int col0 = wg * 64 + c * 32;
         const uint64_t sl2p = f2(sl2, sl2), nlse = f2(-lse2_cur, -lse2_cur), ndlt = f2(-dlt_cur, -dlt_cur);
         uint64_t sum2 = f2(0.f, 0.f);
@@ -654,18 +655,9 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         return x0 + x1;
       };
       uint32_t pk0[16], pk1[16], dk0[16], dk1[16];
-      auto tile_math = [&](auto mode_c) {
-        ds_sum0 = chunk(rs0, rd0, pk0, dk0, 0, mode_c);
-        load_row_stats(it + 1, lse_raw, dlt);  // next tile's statistics: the loads complete under this tile's math
-        ds_sum1 = chunk(rs1, rd1, pk1, dk1, 1, mode_c);
-      };
-      if constexpr (ALIBI) {
-        tile_math(std::integral_constant<int, BWD_ALIBI>{});
-      } else if (mrow) {
-        tile_math(std::integral_constant<int, BWD_MASK>{});
-      } else {
-        tile_math(std::integral_constant<int, BWD_PLAIN>{});
-      }
+      ds_sum0 = chunk(rs0, rd0, pk0, dk0, 0);
+      load_row_stats(it + 1, lse_raw, dlt);  // next tile's statistics: the loads complete under this tile's math
+      ds_sum1 = chunk(rs1, rd1, pk1, dk1, 1);
       // Chunk 0 of the next tile is fetched under the stores below if its S and dP are already there (they were
       // issued when this tile was released).  If not -- a 2-stage ring delivers the next tile late -- the stores
       // must not wait for it: they release this tile's products, which in turn free the stage.
@@ -852,7 +844,7 @@ inline BwdWs bwd_layout(const fb_params* p, const PackPlan& plan) {
   return w;
 }
 
-template <typename T, int D, int RP, int NQ, bool ALIBI>
+template <typename T, int D, int RP, int NQ, int MODE>
 int launch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
   using Cfg = BwdCfg<D, RP, NQ>;
   if constexpr (!Cfg::FITS) {
@@ -939,7 +931,7 @@ int launch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
   a.mask_dtype = p->mask_dtype;
   a.mask_batch_period = p->mask_batch_period;
   a.alibi_slopes = p->alibi_slopes;
-  auto kern = bwd_sm100_kernel<T, D, RP, NQ, ALIBI>;
+  auto kern = bwd_sm100_kernel<T, D, RP, NQ, MODE>;
   // per kernel instantiation and device: raise the dynamic shared-memory limit once
   static std::mutex mu;
   static bool attr_done[64] = {};

@@ -89,20 +89,6 @@ __device__ __forceinline__ void tma_tile_4d(uint32_t dst, const CUtensorMap* m, 
   for (int blk = 0; blk < NB; ++blk) tma_load_4d(dst + blk * 128 * SWB, m, bar, col0 + blk * (SWB / 2), row0, h, b);
 }
 
-#ifdef FB_X_SPIN
-__device__ __forceinline__ bool mbar_wait_x(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
-  for (uint32_t it = 0; it < (1u << 24); ++it) {
-    if (mbar_test_wait(bar, parity)) return true;
-    __nanosleep(20);
-    if ((it & 1023u) == 1023u && *abort_flag) return false;
-  }
-  *abort_flag = 1;
-  if (status) atomicExch(status, FB_DEV_WAIT_TIMEOUT);
-  return false;
-}
-#else
-#define mbar_wait_x mbar_wait
-#endif
 enum { FWD_PLAIN = 0, FWD_MASK = 1, FWD_ALIBI = 2 };
 
 template <typename T, int D, int RP, int NQ, bool ALIBI>
@@ -218,7 +204,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         mbar_wait(q_full, 0, abort_flag, a.status);
         for (int j = 0; j < n_kv; ++j) {
           if (j > 0) {  // the softmax warps hold the logits of the previous key tile in registers
-            mbar_wait_x(s_read, (j - 1) & 1, abort_flag, a.status);
+            mbar_wait(s_read, (j - 1) & 1, abort_flag, a.status);
             tc_fence_after_sync();
           }
           const int ks = j % KST;
@@ -254,7 +240,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int j = 0; j < n_kv; ++j) {
           const int vs = j % VST;
           mbar_wait(v_full + 8 * vs, (j / VST) & 1, abort_flag, a.status);
-          mbar_wait_x(p_ready, j & 1, abort_flag, a.status);
+          mbar_wait(p_ready, j & 1, abort_flag, a.status);
           tc_fence_after_sync();
           const uint32_t vo = vs * Cfg::Q_BYTES;
 #pragma unroll
@@ -297,12 +283,13 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       constexpr int MODE = decltype(mode_c)::value;
       constexpr bool DEAD = decltype(dead_c)::value;
       const int k0 = j * 128;
-      // ---- complete the logits (log2 units for MODE != PLAIN) and take the row maximum, four chains
+      // ---- logits from tensor memory (the load of one 32-column chunk overlaps the arithmetic of the previous
+      // one), completed (log2 units for MODE != PLAIN), and the row maximum, four chains
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       const float abase = slope2 * (float)(k0 - grow);
       const uint64_t sl2p = f2(sl2, sl2);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      const uint32_t tSl = tS + lane_off;
+      auto complete = [&](int c) {
         float mv[32];
         if (MODE == FWD_MASK) {
           const int n = min(32, a.Sk - (k0 + c * 32));
@@ -329,14 +316,24 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             s[c][i] = __float_as_uint(v0);
             s[c][i + 1] = __float_as_uint(v1);
           }
-#ifdef FB_X_NOFMAX3
-          mx4[i & 3] = fmaxf(mx4[i & 3], v0);
-          mx4[(i + 1) & 3] = fmaxf(mx4[(i + 1) & 3], v1);
-#else
           mx4[(i >> 1) & 3] = fmax3(mx4[(i >> 1) & 3], v0, v1);
-#endif
         }
-      }
+      };
+      tmem_ld32(tSl, s[0]);
+      tmem_wait_ld(s[0]);
+      tmem_ld32(tSl + 32, s[1]);
+      complete(0);
+      tmem_wait_ld(s[1]);
+      tmem_ld32(tSl + 64, s[2]);
+      complete(1);
+      tmem_wait_ld(s[2]);
+      tmem_ld32(tSl + 96, s[3]);
+      complete(2);
+      tmem_wait_ld(s[3]);
+      // S is entirely in registers: the tensor core may start on the next key tile
+      tc_fence_before_sync();
+      mbar_arrive_warp(s_read);
+      complete(3);
       float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       if (MODE == FWD_PLAIN) mx *= sl2;  // sl2 > 0
       const float m_new = fmaxf(m_used, mx);
@@ -388,25 +385,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     };
 
-    bool loading = false;  // the TMEM loads of this tile's logits were already issued at the end of the previous tile
     for (int j = 0; j < n_kv; ++j) {
       const int k0 = j * 128;
-      const uint32_t tSl = tS + lane_off;
-      if (!loading) {
-        mbar_wait(s_full, j & 1, abort_flag, a.status);
-        tc_fence_after_sync();
-        tmem_ld32(tSl, s[0]);
-        tmem_ld32(tSl + 32, s[1]);
-        tmem_ld32(tSl + 64, s[2]);
-        tmem_ld32(tSl + 96, s[3]);
-      }
-      tmem_wait_ld(s[0]);
-      tmem_wait_ld(s[1]);
-      tmem_wait_ld(s[2]);
-      tmem_wait_ld(s[3]);
-      // S is entirely in registers: the tensor core may start on the next key tile
-      tc_fence_before_sync();
-      mbar_arrive_warp(s_read);
+      mbar_wait(s_full, j & 1, abort_flag, a.status);
+      tc_fence_after_sync();
       const bool dead = (a.causal && k0 + 127 > q0) || (k0 + 128 > a.Sk);
       if constexpr (ALIBI) {
         if (dead) tile(j, std::integral_constant<int, FWD_ALIBI>{}, std::true_type{});
@@ -417,21 +399,6 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       } else {
         if (dead) tile(j, std::integral_constant<int, FWD_PLAIN>{}, std::true_type{});
         else tile(j, std::integral_constant<int, FWD_PLAIN>{}, std::false_type{});
-      }
-      // The next tile's logits are normally complete by now (they were issued when this tile was released): start
-      // their way into the registers, which are free again, under the hand-off of P.
-      loading = false;
-      if (j + 1 < n_kv) {
-#ifndef FB_X_NOPREFETCH
-        loading = __all_sync(0xffffffffu, mbar_test_wait(s_full, (j + 1) & 1));
-#endif
-        if (loading) {
-          tc_fence_after_sync();
-          tmem_ld32(tSl, s[0]);
-          tmem_ld32(tSl + 32, s[1]);
-          tmem_ld32(tSl + 64, s[2]);
-          tmem_ld32(tSl + 96, s[3]);
-        }
       }
       tmem_wait_st();
       tc_fence_before_sync();

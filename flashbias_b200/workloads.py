@@ -32,7 +32,8 @@ from typing import Optional
 
 import torch
 
-__all__ = ["Workload", "make_workload", "WORKLOADS", "flops_fwd", "flops_bwd", "attended_pairs"]
+__all__ = ["Workload", "make_workload", "make_device_workload", "WORKLOADS", "flops_fwd", "flops_bwd",
+           "attended_pairs"]
 
 
 @dataclass
@@ -82,20 +83,33 @@ def _svd_factors(bias_hqk: torch.Tensor, rank: int):
     return qb.float().contiguous(), kb.float().contiguous()
 
 
+def _generic_factors(B=2, H=4, S=1024, D=32, R=8, **_):
+    return _randn(1004, (B, S, H, R)), _randn(1005, (B, S, H, R))
+
+
 def _generic(B=2, H=4, S=1024, D=32, R=8, dtype=torch.float16, causal=False):
     q, k, v, do = _qkvdo(1, B, S, H, D)
-    qb = _randn(1004, (B, S, H, R))
-    kb = _randn(1005, (B, S, H, R))
+    qb, kb = _generic_factors(B, H, S, D, R)
     return "generic", q, k, v, qb, kb, do, causal, 1.0 / math.sqrt(D), dtype
+
+
+def alibi_slopes(H: int) -> torch.Tensor:
+    """m_h = 2^(-8(h+1)/H) (1_Language_Model/attention_with_alibi_bias.py:8-15)."""
+    return torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], dtype=torch.float32)
+
+
+def _alibi_factors(B=1, H=50, S=8192, D=32, **_):
+    m = alibi_slopes(H)
+    pos = torch.arange(S, dtype=torch.float32)
+    qb = torch.stack([-(m[None, :] * pos[:, None]), torch.ones(S, H)], dim=-1).unsqueeze(0)
+    kb = torch.stack([torch.ones(S, H), m[None, :] * pos[:, None]], dim=-1).unsqueeze(0)
+    return qb.contiguous(), kb.contiguous()
 
 
 def _alibi(B=1, H=50, S=8192, D=32, dtype=torch.bfloat16):
     q, k, v, do = _qkvdo(2, B, S, H, D)
-    m = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], dtype=torch.float32)
-    pos = torch.arange(S, dtype=torch.float32)
-    qb = torch.stack([-(m[None, :] * pos[:, None]), torch.ones(S, H)], dim=-1).unsqueeze(0)
-    kb = torch.stack([torch.ones(S, H), m[None, :] * pos[:, None]], dim=-1).unsqueeze(0)
-    return "alibi", q, k, v, qb.contiguous(), kb.contiguous(), do, True, 1.0 / math.sqrt(D), dtype
+    qb, kb = _alibi_factors(B, H, S, D)
+    return "alibi", q, k, v, qb, kb, do, True, 1.0 / math.sqrt(D), dtype
 
 
 def _swin_table(window: int, H: int, hidden: int = 512) -> torch.Tensor:
@@ -116,33 +130,50 @@ def _swin_table(window: int, H: int, hidden: int = 512) -> torch.Tensor:
     return feat[idx.reshape(-1)].reshape(window * window, window * window, H).permute(2, 0, 1).contiguous()
 
 
+def _swin_factors(B=4096, H=24, window=16, D=32, R=16, **_):
+    return _svd_factors(_swin_table(window, H), R)
+
+
 def _swin(B=4096, H=24, window=16, D=32, R=16, dtype=torch.bfloat16):
     S = window * window
     q, k, v, do = _qkvdo(3, B, S, H, D)
-    qb, kb = _svd_factors(_swin_table(window, H), R)
+    qb, kb = _swin_factors(B, H, window, D, R)
     return "swin", q, k, v, qb, kb, do, False, 1.0 / math.sqrt(D), dtype
 
 
-def _pde(B=2, H=8, S=32768, D=64, alpha=4.0, dtype=torch.bfloat16):
-    q, k, v, do = _qkvdo(4, B, S, H, D)
+def _pde_factors(B=2, H=8, S=32768, D=64, alpha=4.0, **_):
     x = _rand(4004, (B, S, 3))
     n2 = (x * x).sum(-1, keepdim=True)
     one = torch.ones_like(n2)
     qb = torch.cat([-alpha * n2, 2 * alpha * x, one], dim=-1).unsqueeze(2)   # (B,S,1,5)
     kb = torch.cat([one, x, -alpha * n2], dim=-1).unsqueeze(2)
-    return "pde", q, k, v, qb.contiguous(), kb.contiguous(), do, False, 1.0 / math.sqrt(D), dtype
+    return qb.contiguous(), kb.contiguous()
+
+
+def _pde(B=2, H=8, S=32768, D=64, alpha=4.0, dtype=torch.bfloat16):
+    q, k, v, do = _qkvdo(4, B, S, H, D)
+    qb, kb = _pde_factors(B, H, S, D, alpha)
+    return "pde", q, k, v, qb, kb, do, False, 1.0 / math.sqrt(D), dtype
+
+
+def _pairformer_factors(B=1, H=16, S=1536, D=32, R=32, C=128, **_):
+    z = _randn(5004, (S, S, C))
+    w = _randn(5005, (H, C)) / math.sqrt(C)
+    bias = torch.einsum("ijc,hc->hij", z, w)
+    return _svd_factors(bias, R)
 
 
 def _pairformer(B=1, H=16, S=1536, D=32, R=32, C=128, dtype=torch.bfloat16):
     q, k, v, do = _qkvdo(5, B, S, H, D)
-    z = _randn(5004, (S, S, C))
-    w = _randn(5005, (H, C)) / math.sqrt(C)
-    bias = torch.einsum("ijc,hc->hij", z, w)
-    qb, kb = _svd_factors(bias, R)
+    qb, kb = _pairformer_factors(B, H, S, D, R, C)
     return "pairformer", q, k, v, qb, kb, do, False, 1.0 / math.sqrt(D), dtype
 
 
 WORKLOADS = {"generic": _generic, "alibi": _alibi, "swin": _swin, "pde": _pde, "pairformer": _pairformer}
+_FACTORS = {"generic": _generic_factors, "alibi": _alibi_factors, "swin": _swin_factors, "pde": _pde_factors,
+            "pairformer": _pairformer_factors}
+_META = {"generic": (torch.float16, False), "alibi": (torch.bfloat16, True), "swin": (torch.bfloat16, False),
+         "pde": (torch.bfloat16, False), "pairformer": (torch.bfloat16, False)}
 
 
 def make_workload(name: str, **sizes) -> Workload:
@@ -150,6 +181,21 @@ def make_workload(name: str, **sizes) -> Workload:
     nm, q, k, v, qb, kb, do, causal, scale, dtype = WORKLOADS[name](**sizes)
     cast = lambda t: t.to(dtype).contiguous()
     return Workload(nm, cast(q), cast(k), cast(v), cast(qb), cast(kb), cast(do), causal, scale, dtype)
+
+
+def make_device_workload(name: str, device, seed: int = 0, **sizes) -> Workload:
+    """Timing-only variant of ``make_workload``: the factors are the seeded CPU ones, q/k/v/dO are drawn N(0,1)
+    on the device (not bit-identical to the CPU-seeded tensors, which a timing run does not need), so that the
+    large workloads do not spend a minute in the host generator."""
+    dtype, causal = _META[name]
+    qb, kb = _FACTORS[name](**sizes)
+    B, H, D = sizes.get("B", qb.shape[0]), sizes["H"], sizes["D"]
+    S = qb.shape[1]
+    g = torch.Generator(device=device).manual_seed(seed)
+    q, k, v, do = (torch.randn((B, S, H, D), generator=g, device=device, dtype=torch.float32).to(dtype)
+                   for _ in range(4))
+    return Workload(name, q, k, v, qb.to(dtype).to(device), kb.to(dtype).to(device), do, causal,
+                    1.0 / math.sqrt(D), dtype)
 
 
 def attended_pairs(B, H, Sq, Sk, causal) -> int:

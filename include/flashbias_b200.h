@@ -141,6 +141,21 @@ int fb_read_status(const int32_t *status, int32_t *value, void *cuda_stream);
 const char *fb_status_string(int32_t value);
 
 /*
+ * Caller-side glue in one pass: y = T(normalize?(x) * head_scale[h]) with x and y addressed as
+ * ptr[b*stride[0] + h*stride[1] + row*stride[2] + col] (ELEMENT strides, contiguous rows of D in {8, 16, 32,
+ * 64, 128} elements that start on 16-byte boundaries).  x: fp32, fp16 or bf16; y: fp16 or bf16.  normalize != 0
+ * divides every row by max(|row|_2, eps) first (torch.nn.functional.normalize); head_scale is optional (H
+ * fp32 values).  Replaces the .permute(0, 2, 1, 3).contiguous().half() copies -- and, for Swin-V2, the
+ * F.normalize(q) * logit_scale product -- that the reference's call sites run before flash_bias_func
+ * (2_Vision_Transformer/swin_transformer_v2.py:194-199, 4_AlphaFold3/protenix/openfold_local/model/
+ * primitives.py:636-640, flash_bias/benchmark.py:316-317): the result may keep the caller's (B, H, S, D) layout,
+ * because fb_fwd / fb_bwd take the same strides.
+ */
+int fb_prepare_rows(const void *x, int32_t x_dtype, const int64_t *x_stride, void *y, int32_t y_dtype,
+                    const int64_t *y_stride, int32_t B, int32_t H, int32_t S, int32_t D, int32_t normalize,
+                    const float *head_scale, float eps, void *cuda_stream);
+
+/*
  * fb_fwd for callers that cannot allocate device memory.  This entry point has no counterpart in the
  * reference, whose launcher allocates its scratch with torch.
  *

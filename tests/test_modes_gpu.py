@@ -295,6 +295,7 @@ def test_fp16_power_of_two_scale_large_factors_do_not_overflow():
     B, H, S, D = 1, 2, 256, 64
     g = torch.Generator().manual_seed(8)
     q, k, v, do = (torch.randn(B, S, H, D, generator=g).half() for _ in range(4))
+    do = (do.float() * 0.01).half()  # keeps dk_bias = dS^T.q_bias (|q_bias| ~ 8192) inside the fp16 range
     pos = torch.arange(S, dtype=torch.float32)
     big = 8192.0 + 8.0 * (pos % 4)
     qb = torch.stack([-big, torch.ones(S)], dim=-1)[None, :, None, :].expand(1, S, H, 2).contiguous().half()
@@ -315,3 +316,32 @@ def test_fp16_power_of_two_scale_large_factors_do_not_overflow():
     # magnitude, so only a loose relative bound applies here (the point of the case is the range, not this)
     for key, g, want in zip(GRADS[3:], grads[3:], g_ref[3:]):
         check_close(f"fp16_pow2_large/{key}", g, want, torch.float16, rel_l2_tol=2e-2)
+
+
+def test_prepare_bhsd_matches_the_call_site_glue():
+    """The fused cast / normalise / per-head scale against the torch ops of the Swin-V2 call site, and the
+    operator on its strided result against the operator on the permuted, contiguous copy."""
+    from flashbias_b200.layout import prepare_bhsd
+    B, H, S, D = 4, 3, 256, 32
+    g = torch.Generator().manual_seed(55)
+    qkv = torch.randn(3, B, H, S, D, generator=g).cuda()  # fp32, (B, H, S, D) slices of one buffer
+    logit_scale = (torch.rand(H, generator=g) * 2 + 1).cuda()
+    q = prepare_bhsd(qkv[0], torch.float16, normalize=True, head_scale=logit_scale)
+    k = prepare_bhsd(qkv[1], torch.float16, normalize=True)
+    v = prepare_bhsd(qkv[2], torch.float16)
+    q_ref = (torch.nn.functional.normalize(qkv[0], dim=-1) * logit_scale[None, :, None, None]).half().permute(0, 2, 1, 3)
+    k_ref = torch.nn.functional.normalize(qkv[1], dim=-1).half().permute(0, 2, 1, 3)
+    v_ref = qkv[2].half().permute(0, 2, 1, 3)
+    assert q.shape == (B, S, H, D) and not q.is_contiguous()
+    for got, want in ((q, q_ref), (k, k_ref), (v, v_ref)):
+        assert (got.float() - want.float()).abs().max().item() <= 2e-3  # one fp16 ulp of values up to ~3
+    assert torch.equal(v, v_ref)
+    o = flash_bias_func(q, k, v, None, None, None, False, 1.0)
+    o_ref = flash_bias_func(q.contiguous(), k.contiguous(), v.contiguous(), None, None, None, False, 1.0)
+    torch.cuda.synchronize()
+    assert torch.equal(o, o_ref)
+    # bf16 output from a bf16 strided input
+    xb = torch.randn(B, S, H, 64, generator=g).bfloat16().cuda().permute(0, 2, 1, 3)  # (B, H, S, D) view
+    yb = prepare_bhsd(xb, torch.bfloat16, normalize=True)
+    want = torch.nn.functional.normalize(xb.float(), dim=-1).bfloat16().permute(0, 2, 1, 3)
+    assert (yb.float() - want.float()).abs().max().item() <= 8e-3
