@@ -92,12 +92,17 @@ struct BwdCfg {
   static constexpr int KV_BYTES = OFF_V + D_BYTES;
   static constexpr int OFF_STAGE = KV_BYTES;
   static constexpr int TAIL_BYTES = 256 + 8192 + 4 * RCX * 4 + 1024;  // barriers, row sums, centre keys, alignment
-  // One P and one dS buffer: the compute warps keep the 16-bit P and dS of a query tile in registers until the
-  // tile's arithmetic is done and only then wait for the products of the previous tile to release the buffers.
-  // STAGED: a staging tile from which the fp32 dQ tile is reduced into global memory in bulk.
-  static constexpr int BASE_BYTES = KV_BYTES + 2 * TILE128 + TAIL_BYTES;
+  // P and dS buffers: the compute warps keep the 16-bit P and dS of a query tile in registers until the tile's
+  // arithmetic is done and only then store them.  With one buffer pair (NBUF = 1) they first wait for the products
+  // of the previous tile to release it.  Where shared memory allows (head_dim 32 without factor tiles) there are
+  // two pairs, used alternately, and the stores of a tile never wait for the products of the previous one.
+  // STAGED: a staging tile from which the fp32 dQ tile is reduced into global memory in bulk
   // (and a [128][rank] tile for dq_bias, rank <= RC / 2)
   static constexpr int STG_WANT = 128 * D * 4 + 256 * RC;
+  static constexpr int NBUF =
+      (KV_BYTES + 4 * TILE128 + TAIL_BYTES + 2 * STAGE_BYTES + STG_WANT <= 227 * 1024) ? 2 : 1;
+  static constexpr int PDS_STRIDE = 2 * TILE128;  // bytes between the buffer pairs
+  static constexpr int BASE_BYTES = KV_BYTES + NBUF * PDS_STRIDE + TAIL_BYTES;
   static constexpr bool STAGED = BASE_BYTES + 2 * STAGE_BYTES + STG_WANT <= 227 * 1024;
   static constexpr int STG_BYTES = STAGED ? STG_WANT : 0;
   static constexpr int FIXED_BYTES = BASE_BYTES + STG_BYTES;
@@ -105,7 +110,7 @@ struct BwdCfg {
   static constexpr int NSTAGE = (FIXED_BYTES + 3 * STAGE_BYTES <= 227 * 1024) ? 3 : 2;
   static constexpr int OFF_P = OFF_STAGE + NSTAGE * STAGE_BYTES;
   static constexpr int OFF_DS = OFF_P + TILE128;
-  static constexpr int OFF_STG = OFF_DS + TILE128;
+  static constexpr int OFF_STG = OFF_P + NBUF * PDS_STRIDE;
   static constexpr int OFF_BAR = OFF_STG + STG_BYTES;
   static constexpr int OFF_ROWSUM = OFF_BAR + 256;   // 4 x 4 x 128 floats: dS row sums per 32-key group
   static constexpr int OFF_KBC = OFF_ROWSUM + 8192;  // 4 x RCX floats: k_bias of the 4 centre keys
@@ -223,7 +228,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(dp_full, 1);
       mbar_init(sdp_read, 8);  // every compute warp has S and dP of the tile in registers
       mbar_init(all_done, 4);  // one commit per issuing thread
-      mbar_init(pds_free, Cfg::SEP_DKB ? 4 : 3);  // the dV, dK, dQ (and dKb) chains have read P and dS of a query tile
+      for (int i = 0; i < 2; ++i)  // the dV, dK, dQ (and dKb) chains have read P and dS of a query tile (per buffer pair)
+        mbar_init(pds_free + 8 * i, Cfg::SEP_DKB ? 4 : 3);
       for (int i = 0; i < 3; ++i) {
         mbar_init(qdo_full + 8 * i, 1);
         mbar_init(qdo_free + 8 * i, 3);  // S|dP, dV and dK chains read a stage
@@ -281,6 +287,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       auto issue_dQ = [&](int it) {
         const int qb = it % Cfg::NDQ;  // dQ|dQb accumulator of this tile
         const uint32_t tq = tmem + qb * Cfg::DQ_STRIDE;
+        const uint32_t pb = (it % Cfg::NBUF) * Cfg::PDS_STRIDE;  // P/dS buffer pair of this tile
         mbar_wait(pds_ready + 8 * (it & 1), (it >> 1) & 1, abort_flag, a.status);
         if (it >= Cfg::NDQ)  // the drain warpgroup has read the tile that used this accumulator last
           mbar_wait(dq_drained + 8 * qb, (it / Cfg::NDQ - 1) & 1, abort_flag, a.status);
@@ -288,18 +295,18 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
         for (int s = 0; s < 8; ++s) {  // contraction over the 128 keys
           if (Cfg::MERGE_Q) {
-            umma_ss(tq + Cfg::T_DQ, desc_at(kDS, kmajor_step<128>(s)), desc_at(mKKc, mnmajor_step<D>(s)),
+            umma_ss(tq + Cfg::T_DQ, desc_at(kDS, pb + kmajor_step<128>(s)), desc_at(mKKc, mnmajor_step<D>(s)),
                     idQM, s > 0);
           } else {
-            umma_ss(tq + Cfg::T_DQ, desc_at(kDS, kmajor_step<128>(s)), desc_at(mK, mnmajor_step<D>(s)),
+            umma_ss(tq + Cfg::T_DQ, desc_at(kDS, pb + kmajor_step<128>(s)), desc_at(mK, mnmajor_step<D>(s)),
                     idQD, s > 0);
             if (RP)
-              umma_ss(tq + Cfg::T_DQB, desc_at(kDS, kmajor_step<128>(s)),
+              umma_ss(tq + Cfg::T_DQB, desc_at(kDS, pb + kmajor_step<128>(s)),
                       desc_at(mKc, mnmajor_step<Cfg::RCX>(s)), idQC, s > 0);
           }
         }
         umma_commit(dq_full + 8 * qb);
-        umma_commit(pds_free);  // this chain no longer reads dS of the tile
+        umma_commit(pds_free + 8 * (it % Cfg::NBUF));  // this chain no longer reads dS of the tile
       };
 #pragma unroll 1
       for (int it = 0; it < n_it; ++it) {
@@ -345,10 +352,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tc_fence_after_sync();
 #pragma unroll
           for (int s = 0; s < 8; ++s)
-            umma_ss(tmem + Cfg::T_DKB, desc_at(mDST, mnmajor_step<128>(s)), desc_at(mQbT, so + mnmajor_step<RPX>(s)),
-                    idTR, (it > 0 || s > 0) ? 1u : 0u);
+            umma_ss(tmem + Cfg::T_DKB, desc_at(mDST, (it % Cfg::NBUF) * Cfg::PDS_STRIDE + mnmajor_step<128>(s)),
+                    desc_at(mQbT, so + mnmajor_step<RPX>(s)), idTR, (it > 0 || s > 0) ? 1u : 0u);
           umma_commit(qdo_free + 8 * st);  // S|dP and dKb of the tile: this thread is done with its stage
-          umma_commit(pds_free);
+          umma_commit(pds_free + 8 * (it % Cfg::NBUF));
         };
 #pragma unroll 1
         for (int it = 0; it < n_it; ++it) {
@@ -397,27 +404,28 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           const int st = it % Cfg::NSTAGE;
           const uint32_t so = st * Cfg::STAGE_BYTES;
           const uint32_t acc0 = it > 0 ? 1u : 0u;
+          const uint32_t pb = (it % Cfg::NBUF) * Cfg::PDS_STRIDE;  // P/dS buffer pair of this tile
           mbar_wait(qdo_full + 8 * st, (it / Cfg::NSTAGE) & 1, abort_flag, a.status);
           mbar_wait(pds_ready + 8 * (it & 1), (it >> 1) & 1, abort_flag, a.status);
           tc_fence_after_sync();
           if (role == 1) {
 #pragma unroll
             for (int s = 0; s < 8; ++s)  // contraction over the 128 query rows
-              umma_ss(tmem + Cfg::T_DV, desc_at(mP, mnmajor_step<128>(s)), desc_at(mDO, so + mnmajor_step<D>(s)), idTD,
+              umma_ss(tmem + Cfg::T_DV, desc_at(mP, pb + mnmajor_step<128>(s)), desc_at(mDO, so + mnmajor_step<D>(s)), idTD,
                       (acc0 | (s > 0)) ? 1u : 0u);
           } else {
 #pragma unroll
             for (int s = 0; s < 8; ++s) {
               if (Cfg::MERGE_K)
-                umma_ss(tmem + Cfg::T_DK, desc_at(mDS, mnmajor_step<128>(s)),
+                umma_ss(tmem + Cfg::T_DK, desc_at(mDS, pb + mnmajor_step<128>(s)),
                         desc_at(mQQb, so + mnmajor_step<D>(s)), idKM, (acc0 | (s > 0)) ? 1u : 0u);
               else
-                umma_ss(tmem + Cfg::T_DK, desc_at(mDS, mnmajor_step<128>(s)),
+                umma_ss(tmem + Cfg::T_DK, desc_at(mDS, pb + mnmajor_step<128>(s)),
                         desc_at(mQ, so + mnmajor_step<D>(s)), idTD, (acc0 | (s > 0)) ? 1u : 0u);
             }
           }
           umma_commit(qdo_free + 8 * st);
-          umma_commit(pds_free);  // this chain no longer reads P / dS of the tile
+          umma_commit(pds_free + 8 * (it % Cfg::NBUF));  // this chain no longer reads P / dS of the tile
         }
       }
       umma_commit(all_done);  // every MMA of this thread
@@ -670,11 +678,14 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tmem_ld32(tDl, rd0);
         }
       }
-      // the dV, dK and dQ products of the previous query tile have read P and dS
-      if (it >= 1) mbar_wait(pds_free, (it - 1) & 1, abort_flag, a.status);
+      // the dV, dK and dQ products of the query tile that used this buffer pair last have read P and dS
+      if (it >= Cfg::NBUF)
+        mbar_wait(pds_free + 8 * (it % Cfg::NBUF), (it / Cfg::NBUF - 1) & 1, abort_flag, a.status);
+      const uint32_t pb = (it % Cfg::NBUF) * Cfg::PDS_STRIDE;
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
-        const uint32_t o0 = tile_chunk_offset<128>(row, wg * 64 + g * 8), o1 = tile_chunk_offset<128>(row, wg * 64 + 32 + g * 8);
+        const uint32_t o0 = pb + tile_chunk_offset<128>(row, wg * 64 + g * 8),
+                       o1 = pb + tile_chunk_offset<128>(row, wg * 64 + 32 + g * 8);
         st_shared_v4(sP + o0, pk0[g * 4], pk0[g * 4 + 1], pk0[g * 4 + 2], pk0[g * 4 + 3]);
         st_shared_v4(sDS + o0, dk0[g * 4], dk0[g * 4 + 1], dk0[g * 4 + 2], dk0[g * 4 + 3]);
         st_shared_v4(sP + o1, pk1[g * 4], pk1[g * 4 + 1], pk1[g * 4 + 2], pk1[g * 4 + 3]);

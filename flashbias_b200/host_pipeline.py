@@ -60,14 +60,16 @@ def _copy_heads(dst: torch.Tensor, src: torch.Tensor, h0: int, h1: int, kind: in
         raise RuntimeError(f"cudaMemcpy2DAsync failed: {rc}")
 
 
-def plan_chunks(q_shape, q_bias_shape, k_bias_shape, in_bytes: int, chunks: int = 5):
+def plan_chunks(q_shape, q_bias_shape, k_bias_shape, in_bytes: int, chunks: int = 5, min_row_bytes: int = 512):
     """Host logic of the pipeline: along which dimension the work is cut and into which ranges.
 
     Returns (dim, ranges) with dim in {"head", "batch", "none"}.  The dimension is one the factors are not
     shared over, so that a factor gradient belongs to exactly one chunk; a chunk must carry at least ~4 MB of
-    inputs to be worth its launches.
+    inputs to be worth its launches, and a head chunk -- a strided slice of the (B, S, H, D) layout, moved as a
+    2-D copy -- must keep rows of at least `min_row_bytes` (short rows make the copy engine descriptor-bound:
+    a few heads of head_dim 32 are 64..256-byte rows).
     """
-    B, _, H, _ = q_shape
+    B, _, H, D = q_shape
     has_bias = q_bias_shape is not None
     per_head = (not has_bias) or (q_bias_shape[2] == H and k_bias_shape[2] == H)
     per_batch = (not has_bias) or (q_bias_shape[0] == B and k_bias_shape[0] == B)
@@ -78,6 +80,8 @@ def plan_chunks(q_shape, q_bias_shape, k_bias_shape, in_bytes: int, chunks: int 
     else:
         dim, n = "none", 1
     chunks = max(1, min(chunks, n, in_bytes // (4 << 20)))
+    if dim == "head":
+        chunks = max(1, min(chunks, (H * D * 2) // max(min_row_bytes, 1)))
     if chunks == 1:
         return "none", [(0, n)]
     base, extra = divmod(n, chunks)
