@@ -39,6 +39,8 @@ extern "C" {
 
 /* flags */
 #define FB_FLAG_FORCE_GENERAL 1 /* use the shape-generic CUDA-core kernels even where the tensor-core path applies */
+#define FB_FLAG_BWD_QUERY_MAJOR 2 /* backward without factor operands at head_dim 32: use the query-major tensor-core
+                                     kernel instead of the key-major one (cross-checks; same results up to rounding) */
 
 /* error codes (negative); positive return values are cudaError_t */
 #define FB_OK 0
