@@ -493,10 +493,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
           for (int g = 0; g < 4; ++g) rsum[g] = s_rowsum[g * 128 + row];
           const int bq = a.bq_bcast ? 0 : b, hq = a.hq_bcast ? 0 : h;
-          // accumulator laid out (Bq, Hq, query rows padded to whole tiles, R): a tile's rows are contiguous
+          // accumulator laid out (Bq, Hq, query tiles, R, 128 rows): a tile is contiguous and stored rank-major, so
+          // that the threads of a warp (consecutive rows) write consecutive floats of the staging tile
           float* tileb = a.dqb_acc + (bh % a.dqb_slots) * a.dqb_slot_stride +
                          (((int64_t)bq * a.Hq + hq) * a.nq_tiles + (i_begin + it)) * (128 * a.R);
-          float* stgb = reinterpret_cast<float*>(smem + Cfg::OFF_STG + 128 * D * 4) + row * a.R;
+          float* stgb = reinterpret_cast<float*>(smem + Cfg::OFF_STG + 128 * D * 4) + row;
           const int used = 2 * a.R;  // (hi, lo) column groups of the centred factor
 #pragma unroll 1
           for (int c0 = 0; c0 < Cfg::RCX && c0 < used; c0 += 16) {
@@ -510,11 +511,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 float v = __uint_as_float(r[i]);
 #pragma unroll
                 for (int g = 0; g < 4; ++g) v = fmaf(s_kbc[g * Cfg::RCX + c], rsum[g], v);
-                if (Cfg::STAGED) stgb[c] = v;
-                else if (grow < a.Sq) atomicAdd(tileb + row * a.R + c, v);
+                if (Cfg::STAGED) stgb[c * 128] = v;
+                else if (grow < a.Sq) atomicAdd(tileb + c * 128 + row, v);
               } else if (c < used) {
-                if (Cfg::STAGED) stgb[c - a.R] += __uint_as_float(r[i]);
-                else if (grow < a.Sq) atomicAdd(tileb + row * a.R + c - a.R, __uint_as_float(r[i]));
+                if (Cfg::STAGED) stgb[(c - a.R) * 128] += __uint_as_float(r[i]);
+                else if (grow < a.Sq) atomicAdd(tileb + (c - a.R) * 128 + row, __uint_as_float(r[i]));
               }
             }
           }
@@ -742,10 +743,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     }
     if (RP && wg == 0) {
-      // dk_bias tile of this CTA: staged [128][R] in the (now idle) P tile, one bulk reduction into the accumulator
+      // dk_bias tile of this CTA: staged rank-major, [R][128], in the (now idle) P tile, one bulk reduction into the accumulator
       // (other (batch, head) pairs add to the same rows when the factor is shared)
       const int bk = a.bk_bcast ? 0 : b, hk = a.hk_bcast ? 0 : h;
-      float* stg = reinterpret_cast<float*>(smem + Cfg::OFF_P) + row * a.R;
+      float* stg = reinterpret_cast<float*>(smem + Cfg::OFF_P) + row;
       const int used = a.R;
 #pragma unroll 1
       for (int c0 = 0; c0 < RPX && c0 < used; c0 += 16) {
@@ -754,7 +755,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_wait_ld(r);
 #pragma unroll
         for (int i = 0; i < 16; ++i)
-          if (c0 + i < used) stg[c0 + i] = __uint_as_float(r[i]) * a.dkb_scale;
+          if (c0 + i < used) stg[(c0 + i) * 128] = __uint_as_float(r[i]) * a.dkb_scale;
       }
       fence_proxy_async_smem();
       asm volatile("bar.sync 4, 128;" ::: "memory");  // warpgroup 0 only

@@ -328,10 +328,12 @@ __global__ void __launch_bounds__(kWarps * 32) bwd_dkv_general_kernel(const fb_p
 }
 
 // fp32 accumulator -> 16-bit gradient tensor with the factor's own strides.  The accumulator is addressed
-// (b, h, s, r) through element strides (ab, ah, as): (Bx, S, Hx, R) or head-major with padded rows; `slots`
+// (b, h, s, r) through element strides (ab, ah, as, ar): (Bx, S, Hx, R), or -- `tiled` -- head-major in tiles of
+// 128 rows stored rank-major, [r][row in tile] (the tensor-core backward stages its tiles that way: consecutive
+// rows are consecutive floats, which keeps the threads' shared-memory stores free of bank conflicts); `slots`
 // copies at distance `slot_stride` are summed.
 template <typename T>
-__global__ void factor_grad_store_kernel(const float* __restrict__ acc, int64_t ab, int64_t ah, int64_t as,
+__global__ void factor_grad_store_kernel(const float* __restrict__ acc, int64_t ab, int64_t ah, int64_t as, int tiled,
                                          int slots, int64_t slot_stride,
                                          T* __restrict__ out, int Bx, int S, int Hx, int R, int64_t sb, int64_t sh,
                                          int64_t ss) {
@@ -342,7 +344,8 @@ __global__ void factor_grad_store_kernel(const float* __restrict__ acc, int64_t 
   const int h = (int)((idx / R) % Hx);
   const int s = (int)((idx / ((int64_t)R * Hx)) % S);
   const int b = (int)(idx / ((int64_t)R * Hx * S));
-  const float* src = acc + b * ab + h * ah + s * as + r;
+  const float* src = tiled ? acc + b * ab + h * ah + (int64_t)(s / 128) * (128 * R) + r * 128 + (s % 128)
+                           : acc + b * ab + h * ah + s * as + r;
   float v = 0.f;
   for (int e = 0; e < slots; ++e) v += src[e * slot_stride];
   out[b * sb + h * sh + s * ss + r] = from_f32<T>(v);
@@ -362,11 +365,11 @@ static void launch_one_factor_store(const float* acc, FactorAccLayout l, T* out,
   const int64_t n = (int64_t)Bx * S * Hx * R;
   const unsigned blocks = (unsigned)((n + 255) / 256);
   if (l.rows > 0)  // (slots, Bx, Hx, rows, R)
-    factor_grad_store_kernel<T><<<blocks, 256, 0, st>>>(acc, Hx * l.rows * R, l.rows * R, R, l.slots, l.slot_stride,
+    factor_grad_store_kernel<T><<<blocks, 256, 0, st>>>(acc, Hx * l.rows * R, l.rows * R, R, 1, l.slots, l.slot_stride,
                                                         out, Bx, S, Hx, R, stride[0], stride[1], stride[2]);
   else  // (Bx, S, Hx, R)
-    factor_grad_store_kernel<T><<<blocks, 256, 0, st>>>(acc, (int64_t)S * Hx * R, R, (int64_t)Hx * R, 1, 0, out, Bx, S,
-                                                        Hx, R, stride[0], stride[1], stride[2]);
+    factor_grad_store_kernel<T><<<blocks, 256, 0, st>>>(acc, (int64_t)S * Hx * R, R, (int64_t)Hx * R, 0, 1, 0, out, Bx,
+                                                        S, Hx, R, stride[0], stride[1], stride[2]);
 }
 
 template <typename T>

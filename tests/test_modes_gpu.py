@@ -97,7 +97,7 @@ def test_masks_on_tensor_path(case):
     fwd_t, bwd_t = _uses_tensor_path(dev[0], dev[1], dev[2], dev[3], dev[4], mask.cuda(), causal, scale)
     assert fwd_t == 1
     assert bwd_t == (1 if D <= 64 else 0)
-    _check_all("mask", host, mask, causal, scale, dtype)
+    _check_all("mask/B%dH%dSq%dSk%dD%dR%d" % (B, H, Sq, Sk, D, R), host, mask, causal, scale, dtype)
 
 
 @pytest.mark.parametrize("name", ["mask_vector", "mask_matrix"])
@@ -166,10 +166,11 @@ def test_alibi_producer(case):
     qb = torch.stack([-(m[None, :] * pi[:, None]), torch.ones(Sq, H, dtype=f64)], dim=-1).unsqueeze(0)
     kb = torch.stack([torch.ones(Sk, H, dtype=f64), m[None, :] * pj[:, None]], dim=-1).unsqueeze(0)
     o_ref, lse_ref = orc.attention_forward(q, k, v, qb, kb, None, causal, None, dtype=f64)
-    check_close("alibi_producer/o", o, o_ref, dtype)
+    tag = "alibi_producer/B%dH%dSq%dSk%dD%d%s%s" % (B, H, Sq, Sk, D, "c" if causal else "", "g" if flags else "")
+    check_close(f"{tag}/o", o, o_ref, dtype)
     g_ref = orc.attention_backward(do, q, k, v, o.detach().cpu(), lse_ref, qb, kb, None, causal, None, dtype=f64)
     for key, got, want in zip(("dq", "dk", "dv"), (dq, dk, dv), g_ref[:3]):
-        check_close(f"alibi_producer/{key}", got, want, dtype)
+        check_close(f"{tag}/{key}", got, want, dtype)
 
 
 # ---------------------------------------------------------------------------------------------------------------

@@ -160,9 +160,10 @@ def test_tensor_kernel_variants(case):
     torch.cuda.synchronize()
     f32 = [t.float() if t is not None else None for t in host]
     o_ref, lse_ref = orc.attention_forward(f32[0], f32[1], f32[2], f32[3], f32[4], None, causal, scale)
-    check_close("variant/o", o, o_ref, dtype)
+    tag = "variant/B%dH%dSq%dSk%dD%dR%d%s/%s" % (B, H, Sq, Sk, D, R, "c" if causal else "", str(dtype)[6:])
+    check_close(f"{tag}/o", o, o_ref, dtype)
     g_ref = orc.attention_backward(f32[5], f32[0], f32[1], f32[2], o.detach().float().cpu(), lse_ref, f32[3], f32[4],
                                    None, causal, scale)
     for key, t, ref in zip(GRADS, leaves, g_ref):
         if t is not None:
-            check_close(f"variant/{key}", t.grad, ref, dtype)
+            check_close(f"{tag}/{key}", t.grad, ref, dtype)
