@@ -2,10 +2,15 @@
 // tensor memory, warp-specialised roles.  (Kernel and launcher templates; the instantiations are spread
 // over several translation units so that they compile in parallel.)
 //
-// One CTA owns one tile of 128 query rows of one (batch, head) and walks the key/value tiles:
-//   warp 4      TMA producer: barrier set-up and the first loads before the CTA-wide sync; Q (or the (hi, lo)
-//               split of q*scale) | packed q_bias once, then K|packed k_bias and V tiles through rings of
-//               shared-memory stages.
+// The kernel is persistent: the grid is one CTA per resident slot of the GPU, and a CTA walks work items (a tile of
+// 128 query rows of one (batch, head)) with a stride of the grid size, heaviest first under causal masking.  The
+// operand rings, the barrier phases and the tensor-memory allocation carry over from item to item, so the loads of
+// the next item (Q as soon as this item's last logit product has completed, K/V as ring slots free) run under the
+// softmax and the P.V products of this one, and the per-CTA set-up is paid once per SM slot instead of once per
+// query tile -- which is what a short sequence (Swin windows: two key tiles per item) needs.
+// For one item the CTA walks the key/value tiles:
+//   warp 4      TMA producer: Q (or the (hi, lo) split of q*scale) | packed q_bias once per item, then K|packed k_bias
+//               and V tiles through rings of shared-memory stages.
 //   warp 5      MMA issuer (one thread): S = [Q|Qb].[K|Kb]^T into TMEM, bias products first.
 //   warp 6      MMA issuer (one thread, another warp scheduler): O += P.V with P read from TMEM.
 //   warp 7      idle (completes the second warpgroup, which hands most of its registers to the first).
@@ -34,6 +39,7 @@ namespace fb {
 
 struct FwdArgs {
   int B, H, Sq, Sk, nq_tiles, causal;
+  int total_items;  // query tiles x batch x heads: the CTAs walk them with a stride of the grid size
   int hq_bcast, bq_bcast, hk_bcast, bk_bcast;  // 1 = the packed factor has extent 1 on that dim
   float scale, scale_log2;
   void* o;
@@ -116,32 +122,28 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int BH = a.B * a.H;
-  int qt, bh;
-  if (a.causal) {  // heaviest (last) query tiles first
-    qt = a.nq_tiles - 1 - (int)(blockIdx.x / BH);
-    bh = (int)(blockIdx.x % BH);
-  } else {
-    qt = (int)(blockIdx.x % a.nq_tiles);
-    bh = (int)(blockIdx.x / a.nq_tiles);
-  }
-  const int b = bh / a.H, h = bh % a.H;
-  const int q0 = qt * 128;
-  const int kv_end = a.causal ? min(a.Sk, q0 + 128) : a.Sk;
-  const int n_kv = (kv_end + 127) / 128;
+  const uint32_t q_free = bar0 + 184;  // every logit product of an item has completed: Q may be overwritten
+  struct Item {
+    int bh, b, h, q0, n_kv;
+  };
+  auto item_of = [&](int idx) {
+    Item it;
+    int qt;
+    if (a.causal) {  // heaviest (last) query tiles first
+      qt = a.nq_tiles - 1 - idx / BH;
+      it.bh = idx % BH;
+    } else {
+      qt = idx % a.nq_tiles;
+      it.bh = idx / a.nq_tiles;
+    }
+    it.b = it.bh / a.H;
+    it.h = it.bh % a.H;
+    it.q0 = qt * 128;
+    const int kv_end = a.causal ? min(a.Sk, it.q0 + 128) : a.Sk;
+    it.n_kv = (kv_end + 127) / 128;
+    return it;
+  };
 
-  // producer thread only: the K|Kb and V tiles of key tile j
-  const int hk = a.hk_bcast ? 0 : h, bk = a.bk_bcast ? 0 : b;
-  auto load_k = [&](int j) {
-    const int ks = j % KST;
-    mbar_expect_tx(k_full + 8 * ks, Cfg::Q_BYTES + Cfg::QB_BYTES);
-    tma_tile_4d<D>(sK + ks * Cfg::Q_BYTES, &tmK, k_full + 8 * ks, j * 128, h, b);
-    if (RP) tma_tile_4d<RPX>(sKb + ks * Cfg::QB_BYTES, &tmKb, k_full + 8 * ks, j * 128, hk, bk);
-  };
-  auto load_v = [&](int j) {
-    const int vs = j % VST;
-    mbar_expect_tx(v_full + 8 * vs, Cfg::Q_BYTES);
-    tma_tile_4d<D>(sV + vs * Cfg::Q_BYTES, &tmV, v_full + 8 * vs, j * 128, h, b);
-  };
   if (warp == 4) {
     if (lane == 0) {
       *abort_flag = 0;
@@ -156,15 +158,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         mbar_init(v_full + 8 * i, 1);
         mbar_init(v_free + 8 * i, 1);
       }
+      mbar_init(q_free, 1);
       mbar_fence_init();
-      // the first loads start before the rest of the CTA has finished its set-up
-      const int hq = a.hq_bcast ? 0 : h, bq = a.bq_bcast ? 0 : b;
-      mbar_expect_tx(q_full, NQ * Cfg::Q_BYTES + Cfg::QB_BYTES);
-#pragma unroll
-      for (int t = 0; t < NQ; ++t) tma_tile_4d<D>(sQ + t * Cfg::Q_BYTES, &tmQ, q_full, q0, h, b, t * D);
-      if (RP) tma_tile_4d<RPX>(sQb, &tmQb, q_full, q0, hq, bq);
-      for (int j = 0; j < KST && j < n_kv; ++j) load_k(j);
-      for (int j = 0; j < VST && j < n_kv; ++j) load_v(j);
     }
   } else if (warp == 5) {
     tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
@@ -183,14 +178,25 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (warp == 4) {
       // ------------------------------------------------------------------ TMA producer
       if (lane == 0) {
-        for (int j = min(KST, VST); j < n_kv; ++j) {
-          if (j >= KST) {
-            mbar_wait(k_free + 8 * (j % KST), ((j / KST) - 1) & 1, abort_flag, a.status);
-            load_k(j);
-          }
-          if (j >= VST) {
-            mbar_wait(v_free + 8 * (j % VST), ((j / VST) - 1) & 1, abort_flag, a.status);
-            load_v(j);
+        int kc = 0, vc = 0, n = 0;  // K and V tiles loaded so far (ring positions), items started
+        for (int idx = blockIdx.x; idx < a.total_items; idx += gridDim.x, ++n) {
+          const Item it = item_of(idx);
+          const int hq = a.hq_bcast ? 0 : it.h, bq = a.bq_bcast ? 0 : it.b;
+          const int hk = a.hk_bcast ? 0 : it.h, bk = a.bk_bcast ? 0 : it.b;
+          if (n > 0) mbar_wait(q_free, (n - 1) & 1, abort_flag, a.status);
+          mbar_expect_tx(q_full, NQ * Cfg::Q_BYTES + Cfg::QB_BYTES);
+#pragma unroll
+          for (int t = 0; t < NQ; ++t) tma_tile_4d<D>(sQ + t * Cfg::Q_BYTES, &tmQ, q_full, it.q0, it.h, it.b, t * D);
+          if (RP) tma_tile_4d<RPX>(sQb, &tmQb, q_full, it.q0, hq, bq);
+          for (int j = 0; j < it.n_kv; ++j, ++kc, ++vc) {
+            const int ks = kc % KST, vs = vc % VST;
+            if (kc >= KST) mbar_wait(k_free + 8 * ks, ((kc / KST) - 1) & 1, abort_flag, a.status);
+            mbar_expect_tx(k_full + 8 * ks, Cfg::Q_BYTES + Cfg::QB_BYTES);
+            tma_tile_4d<D>(sK + ks * Cfg::Q_BYTES, &tmK, k_full + 8 * ks, j * 128, it.h, it.b);
+            if (RP) tma_tile_4d<RPX>(sKb + ks * Cfg::QB_BYTES, &tmKb, k_full + 8 * ks, j * 128, hk, bk);
+            if (vc >= VST) mbar_wait(v_free + 8 * vs, ((vc / VST) - 1) & 1, abort_flag, a.status);
+            mbar_expect_tx(v_full + 8 * vs, Cfg::Q_BYTES);
+            tma_tile_4d<D>(sV + vs * Cfg::Q_BYTES, &tmV, v_full + 8 * vs, j * 128, it.h, it.b);
           }
         }
       }
@@ -201,33 +207,38 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         // descriptor views built once; each MMA only adds a constant to the start-address field
         const DescBase dQ = kmajor_base<D>(sQ), dQb = kmajor_base<RPX>(sQb), dK = kmajor_base<D>(sK),
                        dKb = kmajor_base<RPX>(sKb);
-        mbar_wait(q_full, 0, abort_flag, a.status);
-        for (int j = 0; j < n_kv; ++j) {
-          if (j > 0) {  // the softmax warps hold the logits of the previous key tile in registers
-            mbar_wait(s_read, (j - 1) & 1, abort_flag, a.status);
+        int t = 0, n = 0;  // key tiles and items issued so far
+        for (int idx = blockIdx.x; idx < a.total_items; idx += gridDim.x, ++n) {
+          const Item it = item_of(idx);
+          mbar_wait(q_full, n & 1, abort_flag, a.status);
+          for (int j = 0; j < it.n_kv; ++j, ++t) {
+            if (t > 0) {  // the softmax warps hold the logits of the previous key tile in registers
+              mbar_wait(s_read, (t - 1) & 1, abort_flag, a.status);
+              tc_fence_after_sync();
+            }
+            const int ks = t % KST;
+            mbar_wait(k_full + 8 * ks, (t / KST) & 1, abort_flag, a.status);
             tc_fence_after_sync();
-          }
-          const int ks = j % KST;
-          mbar_wait(k_full + 8 * ks, (j / KST) & 1, abort_flag, a.status);
-          tc_fence_after_sync();
-          const uint32_t ko = ks * Cfg::Q_BYTES, kbo = ks * Cfg::QB_BYTES;
-          // The bias products go first, into the empty accumulator: factor terms as large as a sequence
-          // position then only meet each other (and cancel exactly), instead of forcing the small q.k sum to be
-          // aligned to their magnitude inside the tensor core's adder.
-          if (RP) {
+            const uint32_t ko = ks * Cfg::Q_BYTES, kbo = ks * Cfg::QB_BYTES;
+            // The bias products go first, into the empty accumulator: factor terms as large as a sequence
+            // position then only meet each other (and cancel exactly), instead of forcing the small q.k sum to be
+            // aligned to their magnitude inside the tensor core's adder.
+            if (RP) {
 #pragma unroll
-            for (int s = 0; s < RPX / 16; ++s)
-              umma_ss(tS, desc_at(dQb, kmajor_step<RPX>(s)), desc_at(dKb, kbo + kmajor_step<RPX>(s)), idS, s > 0);
-          }
+              for (int s = 0; s < RPX / 16; ++s)
+                umma_ss(tS, desc_at(dQb, kmajor_step<RPX>(s)), desc_at(dKb, kbo + kmajor_step<RPX>(s)), idS, s > 0);
+            }
 #pragma unroll
-          for (int t = 0; t < NQ; ++t) {  // query terms share the K tile
+            for (int q = 0; q < NQ; ++q) {  // query terms share the K tile
 #pragma unroll
-            for (int s = 0; s < D / 16; ++s)
-              umma_ss(tS, desc_at(dQ, t * Cfg::Q_BYTES + kmajor_step<D>(s)), desc_at(dK, ko + kmajor_step<D>(s)), idS,
-                      (RP || t > 0 || s > 0) ? 1u : 0u);
+              for (int s = 0; s < D / 16; ++s)
+                umma_ss(tS, desc_at(dQ, q * Cfg::Q_BYTES + kmajor_step<D>(s)), desc_at(dK, ko + kmajor_step<D>(s)),
+                        idS, (RP || q > 0 || s > 0) ? 1u : 0u);
+            }
+            umma_commit(s_full);
+            umma_commit(k_free + 8 * ks);
           }
-          umma_commit(s_full);
-          umma_commit(k_free + 8 * ks);
+          umma_commit(q_free);  // Q | Qb of this item are no longer read
         }
       }
     } else if (warp == 6) {
@@ -237,17 +248,21 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (lane == 0) {
         constexpr uint32_t idO = instr_desc(kBf16, false, true, 128, D);
         const DescBase dV = mnmajor_base<D>(sV);
-        for (int j = 0; j < n_kv; ++j) {
-          const int vs = j % VST;
-          mbar_wait(v_full + 8 * vs, (j / VST) & 1, abort_flag, a.status);
-          mbar_wait(p_ready, j & 1, abort_flag, a.status);
-          tc_fence_after_sync();
-          const uint32_t vo = vs * Cfg::Q_BYTES;
+        int t = 0;
+        for (int idx = blockIdx.x; idx < a.total_items; idx += gridDim.x) {
+          const Item it = item_of(idx);
+          for (int j = 0; j < it.n_kv; ++j, ++t) {
+            const int vs = t % VST;
+            mbar_wait(v_full + 8 * vs, (t / VST) & 1, abort_flag, a.status);
+            mbar_wait(p_ready, t & 1, abort_flag, a.status);
+            tc_fence_after_sync();
+            const uint32_t vo = vs * Cfg::Q_BYTES;
 #pragma unroll
-          for (int s = 0; s < 8; ++s)
-            umma_ts(tO, tP + s * 8, desc_at(dV, vo + mnmajor_step<D>(s)), idO, (j > 0 || s > 0) ? 1u : 0u);
-          umma_commit(pv_done);
-          umma_commit(v_free + 8 * vs);
+            for (int s = 0; s < 8; ++s)
+              umma_ts(tO, tP + s * 8, desc_at(dV, vo + mnmajor_step<D>(s)), idO, (j > 0 || s > 0) ? 1u : 0u);
+            umma_commit(pv_done);
+            umma_commit(v_free + 8 * vs);
+          }
         }
       }
     }
@@ -256,25 +271,16 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if constexpr (Cfg::MINB == 2) setmaxnreg_inc<208>();
     constexpr float kLog2e = 1.4426950408889634f;
     const int row = warp * 32 + lane;
-    const int grow = q0 + row;
     const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
     const float sl2 = a.scale_log2;
-    // running reference maximum and row sum; both in units of log2 (logit * log2 e)
-    float m_used = -INFINITY, l = 0.f;
-    float slope2 = 0.f;  // ALiBi slope of this head, times log2 e
-    if (ALIBI) slope2 = __ldg(a.alibi_slopes + h) * kLog2e;
-    // additive mask: this thread's row
-    const char* mrow = nullptr;
+    // state of the current work item
+    int q0 = 0, grow = 0;
+    float m_used = -INFINITY, l = 0.f;  // running reference maximum and row sum, in units of log2 (logit * log2 e)
+    float slope2 = 0.f;                 // ALiBi slope of this head, times log2 e
+    const char* mrow = nullptr;         // additive mask: this thread's row
     int msize = 4;
     bool mvec = false;
-    if (!ALIBI && a.mask_kind != FB_MASK_NONE) {
-      msize = a.mask_dtype == FB_DTYPE_F32 ? 4 : 2;
-      const int mb = a.mask_batch_period > 0 ? b % a.mask_batch_period : b;
-      const int64_t off = mb * a.mask_stride[0] + h * a.mask_stride[1] +
-                          (int64_t)min(grow, a.Sq - 1) * a.mask_stride[2];
-      mrow = reinterpret_cast<const char*>(a.mask) + off * msize;
-      mvec = (reinterpret_cast<uintptr_t>(mrow) & 15) == 0;
-    }
+    int t = 0;  // key tiles processed so far by this CTA (barrier phases run across work items)
     uint32_t s[4][32];  // the thread's row of the logit tile
 
     // One key tile.  MODE: how the logits are completed (plain / + mask tensor / + ALiBi term);
@@ -338,7 +344,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (MODE == FWD_PLAIN) mx *= sl2;  // sl2 > 0
       const float m_new = fmaxf(m_used, mx);
       if (j > 0) {
-        mbar_wait(pv_done, (j - 1) & 1, abort_flag, a.status);  // P buffer free, O stable
+        mbar_wait(pv_done, (t - 1) & 1, abort_flag, a.status);  // P buffer free, O stable
         tc_fence_after_sync();
         const bool grow_needed = m_new - m_used > 8.f;
         if (__any_sync(0xffffffffu, grow_needed)) {
@@ -385,9 +391,25 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     };
 
-    for (int j = 0; j < n_kv; ++j) {
+    for (int idx = blockIdx.x; idx < a.total_items; idx += gridDim.x) {
+    const Item item = item_of(idx);
+    const int b = item.b, h = item.h, bh = item.bh, n_kv = item.n_kv;
+    q0 = item.q0;
+    grow = q0 + row;
+    m_used = -INFINITY;
+    l = 0.f;
+    if (ALIBI) slope2 = __ldg(a.alibi_slopes + h) * kLog2e;
+    if (!ALIBI && a.mask_kind != FB_MASK_NONE) {
+      msize = a.mask_dtype == FB_DTYPE_F32 ? 4 : 2;
+      const int mb = a.mask_batch_period > 0 ? b % a.mask_batch_period : b;
+      const int64_t off = mb * a.mask_stride[0] + h * a.mask_stride[1] +
+                          (int64_t)min(grow, a.Sq - 1) * a.mask_stride[2];
+      mrow = reinterpret_cast<const char*>(a.mask) + off * msize;
+      mvec = (reinterpret_cast<uintptr_t>(mrow) & 15) == 0;
+    }
+    for (int j = 0; j < n_kv; ++j, ++t) {
       const int k0 = j * 128;
-      mbar_wait(s_full, j & 1, abort_flag, a.status);
+      mbar_wait(s_full, t & 1, abort_flag, a.status);
       tc_fence_after_sync();
       const bool dead = (a.causal && k0 + 127 > q0) || (k0 + 128 > a.Sk);
       if constexpr (ALIBI) {
@@ -405,7 +427,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_arrive_warp(p_ready);
     }
     // ---- epilogue: O / l -> global, lse
-    mbar_wait(pv_done, (n_kv - 1) & 1, abort_flag, a.status);
+    mbar_wait(pv_done, (t - 1) & 1, abort_flag, a.status);
     tc_fence_after_sync();
     const float inv = l > 0.f ? 1.f / l : 0.f;
     T* orow = reinterpret_cast<T*>(a.o) + b * a.o_stride[0] + h * a.o_stride[1] + (int64_t)grow * a.o_stride[2];
@@ -431,6 +453,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       a.lse[(int64_t)bh * a.lse_stride_bh + grow] =
           l > 0.f ? (m_used + fast_log2(l)) * 0.6931471805599453f : -INFINITY;
     }
+    // the reads of O above are complete before the next item's first P.V product (issued after this warp's next
+    // arrival on p_ready) overwrites the accumulator
+    tc_fence_before_sync();
+    }  // work items
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -487,6 +513,7 @@ int launch_fwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
     FwdArgs a;
     a.B = p->B; a.H = p->H; a.Sq = p->Sq; a.Sk = p->Sk;
     a.nq_tiles = (p->Sq + 127) / 128;
+    a.total_items = (int)((int64_t)a.nq_tiles * p->B * p->H);
     a.causal = p->causal;
     a.hq_bcast = plan.Hq == 1; a.bq_bcast = plan.Bq == 1; a.hk_bcast = plan.Hk == 1; a.bk_bcast = plan.Bk == 1;
     // logits = a.scale * S: the scale is already inside the query operand when it is split
@@ -507,18 +534,23 @@ int launch_fwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
     auto kern = fwd_sm100_kernel<T, D, RP, NQ, ALIBI>;
     // per kernel instantiation and device: raise the dynamic shared-memory limit once
     static std::mutex mu;
-    static bool attr_done[64] = {};
+    static int sm_count[64] = {};  // 0: not set up on that device yet
     int dev = 0;
     cudaGetDevice(&dev);
     {
       std::lock_guard<std::mutex> lk(mu);
-      if (!attr_done[dev & 63]) {
+      if (!sm_count[dev & 63]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
         if (e != cudaSuccess) return (int)e;
-        attr_done[dev & 63] = true;
+        int n = 0;
+        e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess || n <= 0) return e != cudaSuccess ? (int)e : FB_ENOTBUILT;
+        sm_count[dev & 63] = n;
       }
     }
-    const unsigned grid = (unsigned)((int64_t)a.nq_tiles * p->B * p->H);
+    // persistent: one CTA per resident slot (or fewer, if there are fewer work items)
+    const int slots = sm_count[dev & 63] * Cfg::MINB;
+    const unsigned grid = (unsigned)(a.total_items < slots ? a.total_items : slots);
     prof_before(KC_FWD_MAIN, st);
     kern<<<grid, 256, Cfg::SMEM, st>>>(tQ, tK, tV, tQb, tKb, a);
     prof_after(KC_FWD_MAIN, st);
