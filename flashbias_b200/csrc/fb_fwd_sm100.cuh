@@ -126,6 +126,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   struct Item {
     int bh, b, h, q0, n_kv;
   };
+  // The w-th work item of this CTA.  Items are ordered heaviest first (causal); the CTAs take them in snake order
+  // (0..G-1, then G-1..0, ...), which evens out the sums of a decreasing sequence much better than a plain stride.
+  auto item_index = [&](int w) {
+    const int G = (int)gridDim.x, c = (int)blockIdx.x;
+    return w * G + ((w & 1) ? G - 1 - c : c);
+  };
   auto item_of = [&](int idx) {
     Item it;
     int qt;
@@ -179,7 +185,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       // ------------------------------------------------------------------ TMA producer
       if (lane == 0) {
         int kc = 0, vc = 0, n = 0;  // K and V tiles loaded so far (ring positions), items started
-        for (int idx = blockIdx.x; idx < a.total_items; idx += gridDim.x, ++n) {
+        for (int w = 0, idx; (idx = item_index(w)) < a.total_items; ++w, ++n) {
           const Item it = item_of(idx);
           const int hq = a.hq_bcast ? 0 : it.h, bq = a.bq_bcast ? 0 : it.b;
           const int hk = a.hk_bcast ? 0 : it.h, bk = a.bk_bcast ? 0 : it.b;
@@ -208,7 +214,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const DescBase dQ = kmajor_base<D>(sQ), dQb = kmajor_base<RPX>(sQb), dK = kmajor_base<D>(sK),
                        dKb = kmajor_base<RPX>(sKb);
         int t = 0, n = 0;  // key tiles and items issued so far
-        for (int idx = blockIdx.x; idx < a.total_items; idx += gridDim.x, ++n) {
+        for (int w = 0, idx; (idx = item_index(w)) < a.total_items; ++w, ++n) {
           const Item it = item_of(idx);
           mbar_wait(q_full, n & 1, abort_flag, a.status);
           for (int j = 0; j < it.n_kv; ++j, ++t) {
@@ -249,7 +255,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         constexpr uint32_t idO = instr_desc(kBf16, false, true, 128, D);
         const DescBase dV = mnmajor_base<D>(sV);
         int t = 0;
-        for (int idx = blockIdx.x; idx < a.total_items; idx += gridDim.x) {
+        for (int w = 0, idx; (idx = item_index(w)) < a.total_items; ++w) {
           const Item it = item_of(idx);
           for (int j = 0; j < it.n_kv; ++j, ++t) {
             const int vs = t % VST;
@@ -391,7 +397,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     };
 
-    for (int idx = blockIdx.x; idx < a.total_items; idx += gridDim.x) {
+    for (int w = 0, idx; (idx = item_index(w)) < a.total_items; ++w) {
     const Item item = item_of(idx);
     const int b = item.b, h = item.h, bh = item.bh, n_kv = item.n_kv;
     q0 = item.q0;
