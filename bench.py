@@ -66,9 +66,9 @@ CPU_SAMPLE = {
 }
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the backward main kernel, per workload: taken from
-# the ncu captures of the reduced cases (PROFILE_SIZES; summaries under profiles/fwd_bwd_sm100_*_small_ncu_full.md)
-# and scaled to the full workload by the number of (batch, head, row) units - the tiles a CTA re-streams (Q, dO per
-# key tile) are served by L2 in both sizes, so DRAM traffic grows with the rows, not with the tile pairs
+# the ncu captures of the reduced cases (PROFILE_SIZES, `--profile-case`) and scaled to the full workload by the
+# number of (batch, head, row) units - the tiles a CTA re-streams (Q, dO per key tile) are served by L2 at both
+# sizes, so DRAM traffic grows with the rows, not with the tile pairs
 NCU_BWD_TRAFFIC_BYTES = {
     "alibi": (47.8e6 + 0.112e6) * (50 * 8192) / (16 * 4096),
     "swin": (825.6e6 + 374.4e6) * 4096 / 256,

@@ -16,6 +16,8 @@ FB_DTYPE_F16, FB_DTYPE_BF16, FB_DTYPE_F32 = 0, 1, 2
 FB_MASK_NONE, FB_MASK_VECTOR, FB_MASK_MATRIX = 0, 1, 2
 FB_FLAG_FORCE_GENERAL = 1
 FB_FLAG_BWD_QUERY_MAJOR = 2
+FB_FLAG_BWD_ONE_ITEM = 4
+FB_FLAG_BWD_PERSISTENT = 8
 
 I64x3 = C.c_int64 * 3
 

@@ -22,7 +22,7 @@ LIB = os.path.join(PKG, "libflashbias_b200.so")
 
 SOURCES = ["fb_api.cu", "fb_tmap.cu", "fb_pack.cu", "fb_general.cu", "fb_selftest.cu",
            "fb_fwd_sm100.cu", "fb_fwd_inst_d32.cu", "fb_fwd_inst_d64.cu", "fb_fwd_inst_d128.cu",
-           "fb_bwd_sm100.cu", "fb_bwd_inst_d32.cu", "fb_bwd_inst_d64.cu", "fb_noalloc.cu", "fb_prepare.cu"]
+           "fb_bwd_sm100.cu", "fb_bwd_inst_d32.cu", "fb_bwd_inst_d32p.cu", "fb_bwd_inst_d64.cu", "fb_noalloc.cu", "fb_prepare.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--use_fast_math", "-Xcompiler", "-fPIC", "-I", os.path.join(ROOT, "include"), "-I", CSRC]
 

@@ -83,6 +83,18 @@ static cudaEvent_t g_prof_open = nullptr;
 
 void note_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
+int device_sm_count(int dev) {
+  static std::mutex mu;
+  static int cached[64] = {};
+  std::lock_guard<std::mutex> lk(mu);
+  int& n = cached[dev & 63];
+  if (!n) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) n = v;
+  }
+  return n;
+}
+
 void prof_before(int kernel_class, cudaStream_t st) {
   if (!g_prof_class) return;
   std::lock_guard<std::mutex> lk(g_prof_mu);

@@ -42,7 +42,21 @@ bool bwd_sm100_supported(const fb_params* p, PackPlan* plan) {
 
 size_t bwd_sm100_workspace(const fb_params* p, const PackPlan& plan) { return bwd_layout(p, plan).total; }
 
+// Whether the persistent form of the query-major kernel is the better one: few query tiles per work item (a CTA
+// that handles one item then spends more time starting and draining than on its tiles) and more items than SMs.
+static bool bwd_prefers_persistent(const fb_params* p) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const int sms = device_sm_count(dev);
+  const int nq = (p->Sq + 127) / 128, nk = (p->Sk + 127) / 128;
+  const int tiles_per_item = p->causal ? (nq + 1) / 2 : nq;  // mean, under causal masking
+  return sms > 0 && tiles_per_item <= 8 && (int64_t)nk * p->B * p->H >= 2 * (int64_t)sms;
+}
+
 int launch_bwd_sm100(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
+  if (p->D == 32 && plan.RP > 0 && !p->alibi_slopes && !(p->flags & FB_FLAG_BWD_ONE_ITEM) &&
+      ((p->flags & FB_FLAG_BWD_PERSISTENT) || bwd_prefers_persistent(p)))
+    return dispatch_bwd_d32p(p, plan, st);
   return p->D == 32 ? dispatch_bwd_d32(p, plan, st) : p->D == 64 ? dispatch_bwd_d64(p, plan, st) : FB_ENOTBUILT;
 }
 

@@ -856,12 +856,17 @@ inline BwdWs bwd_layout(const fb_params* p, const PackPlan& plan) {
   return w;
 }
 
-template <typename T, int D, int RP, int NQ, int MODE>
-int launch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
+// everything a launch of a backward main kernel needs: tensor maps and arguments
+struct BwdLaunch {
+  CUtensorMap tQ, tK, tV, tDO, tQb, tKb, tKc, tKs;
+  BwdArgs a;
+};
+
+// Host work before the main kernel: packs the factor operands, zeroes the fp32 accumulators, encodes the tensor
+// maps and fills the kernel arguments.
+template <typename T, int D, int RP, int NQ>
+int bwd_prepare(const fb_params* p, const PackPlan& plan, cudaStream_t st, BwdLaunch& L) {
   using Cfg = BwdCfg<D, RP, NQ>;
-  if constexpr (!Cfg::FITS) {
-    return FB_ENOTBUILT;
-  } else {
   int rc;
   const BwdWs w = bwd_layout(p, plan);
   uint8_t* ws = reinterpret_cast<uint8_t*>(p->workspace);
@@ -871,7 +876,7 @@ int launch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
   if ((rc = launch_pack_operands(p, plan, qpack, kpack, kcenter, true, ws + w.off_qs, st))) return rc;
   cudaError_t e = cudaMemsetAsync(ws + w.off_dq, 0, w.zero_bytes, st);
   if (e != cudaSuccess) return (int)e;
-  CUtensorMap tQ, tK, tV, tDO, tQb, tKb, tKc, tKs;
+  CUtensorMap &tQ = L.tQ, &tK = L.tK, &tV = L.tV, &tDO = L.tDO, &tQb = L.tQb, &tKb = L.tKb, &tKc = L.tKc, &tKs = L.tKs;
   if ((rc = make_tmap_4d(&tQ, p->q, D, p->Sq, p->H, p->B, p->q_stride[2], p->q_stride[1], p->q_stride[0], D, 128)))
     return rc;
   if (NQ == 2) {
@@ -905,7 +910,7 @@ int launch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
     tKb = tK;
     tKc = tK;
   }
-  BwdArgs a;
+  BwdArgs& a = L.a;
   a.B = p->B; a.H = p->H; a.Sq = p->Sq; a.Sk = p->Sk;
   a.nq_tiles = (p->Sq + 127) / 128;
   a.nk_tiles = (p->Sk + 127) / 128;
@@ -943,6 +948,39 @@ int launch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
   a.mask_dtype = p->mask_dtype;
   a.mask_batch_period = p->mask_batch_period;
   a.alibi_slopes = p->alibi_slopes;
+  return 0;
+}
+
+// Host work after the main kernel: dq and the factor gradients leave their fp32 accumulators.
+template <typename T, int D, int RP, int NQ>
+int bwd_finish(const fb_params* p, const BwdLaunch& L, cudaStream_t st) {
+  using Cfg = BwdCfg<D, RP, NQ>;
+  const BwdArgs& a = L.a;
+  cudaError_t e;
+  const int64_t n8 = ((int64_t)p->B * p->Sq * p->H * D) / 8;
+  dq_store_kernel<T><<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(
+      a.dq_acc, reinterpret_cast<T*>(p->dq), p->B, p->Sq, p->H, D, p->dq_stride[0], p->dq_stride[1], p->dq_stride[2],
+      p->softmax_scale, Cfg::STAGED ? 1 : 0);
+  note_launch();
+  if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
+  if (p->R > 0)
+    return store_factor_grads_from(p, a.dqb_acc, a.dkb_acc, st,
+                                   {(int64_t)a.nq_tiles * 128, a.dqb_slots, a.dqb_slot_stride},
+                                   {(int64_t)a.nk_tiles * 128, a.dkb_slots, a.dkb_slot_stride});
+  return 0;
+}
+
+template <typename T, int D, int RP, int NQ, int MODE>
+int launch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
+  using Cfg = BwdCfg<D, RP, NQ>;
+  if constexpr (!Cfg::FITS) {
+    return FB_ENOTBUILT;
+  } else {
+  int rc;
+  cudaError_t e;
+  BwdLaunch L;
+  if ((rc = bwd_prepare<T, D, RP, NQ>(p, plan, st, L))) return rc;
+  const BwdArgs& a = L.a;
   auto kern = bwd_sm100_kernel<T, D, RP, NQ, MODE>;
   // per kernel instantiation and device: raise the dynamic shared-memory limit once
   static std::mutex mu;
@@ -959,26 +997,18 @@ int launch_bwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
   }
   const unsigned grid = (unsigned)((int64_t)a.nk_tiles * p->B * p->H);
   prof_before(KC_BWD_MAIN, st);
-  kern<<<grid, 512, Cfg::SMEM, st>>>(tQ, tK, tV, tDO, tQb, tKb, tKc, tKs, a);
+  kern<<<grid, 512, Cfg::SMEM, st>>>(L.tQ, L.tK, L.tV, L.tDO, L.tQb, L.tKb, L.tKc, L.tKs, a);
   prof_after(KC_BWD_MAIN, st);
   note_launch();
   if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
-  const int64_t n8 = ((int64_t)p->B * p->Sq * p->H * D) / 8;
-  dq_store_kernel<T><<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(
-      a.dq_acc, reinterpret_cast<T*>(p->dq), p->B, p->Sq, p->H, D, p->dq_stride[0], p->dq_stride[1], p->dq_stride[2],
-      p->softmax_scale, Cfg::STAGED ? 1 : 0);
-  note_launch();
-  if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;
-  if (p->R > 0)
-    return store_factor_grads_from(p, a.dqb_acc, a.dkb_acc, st,
-                                   {(int64_t)a.nq_tiles * 128, a.dqb_slots, a.dqb_slot_stride},
-                                   {(int64_t)a.nk_tiles * 128, a.dkb_slots, a.dkb_slot_stride});
-  return 0;
+  return bwd_finish<T, D, RP, NQ>(p, L, st);
   }
 }
 
 bool bwd_cfg_fits(int D, int RP, int nq);
 int dispatch_bwd_d32(const fb_params* p, const PackPlan& plan, cudaStream_t st);
 int dispatch_bwd_d64(const fb_params* p, const PackPlan& plan, cudaStream_t st);
+// persistent form (head_dim 32 with factor operands, plain or masked logits)
+int dispatch_bwd_d32p(const fb_params* p, const PackPlan& plan, cudaStream_t st);
 
 }  // namespace fb

@@ -76,6 +76,8 @@ int store_factor_grads_from(const fb_params* p, float* dqb, float* dkb, cudaStre
 // of CUDA events is recorded around each launch of that class on the launching stream.
 enum KernelClass { KC_OTHER = 0, KC_FWD_MAIN = 1, KC_BWD_MAIN = 2, KC_BWD_PREPROCESS = 3 };
 void note_launch(int n = 1);
+// number of SMs of a device (cached per device); 0 if the query fails
+int device_sm_count(int dev);
 void prof_before(int kernel_class, cudaStream_t st);
 void prof_after(int kernel_class, cudaStream_t st);
 

@@ -41,6 +41,10 @@ extern "C" {
 #define FB_FLAG_FORCE_GENERAL 1 /* use the shape-generic CUDA-core kernels even where the tensor-core path applies */
 #define FB_FLAG_BWD_QUERY_MAJOR 2 /* backward without factor operands at head_dim 32: use the query-major tensor-core
                                      kernel instead of the key-major one (cross-checks; same results up to rounding) */
+#define FB_FLAG_BWD_ONE_ITEM 4   /* backward with factor operands at head_dim 32: one work item (128 keys of a (batch,
+                                     head)) per CTA, whatever the shape */
+#define FB_FLAG_BWD_PERSISTENT 8 /* ... one persistent CTA per SM walking the work items, whatever the shape (by
+                                     default: chosen when a work item has few query tiles) */
 
 /* error codes (negative); positive return values are cudaError_t */
 #define FB_OK 0

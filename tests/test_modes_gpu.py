@@ -237,6 +237,54 @@ def test_factors_shared_over_batch_and_heads_many_pairs():
 
 
 # ---------------------------------------------------------------------------------------------------------------
+# the two forms of the query-major backward (one work item per CTA / one persistent CTA per SM)
+# ---------------------------------------------------------------------------------------------------------------
+# (B, H, Sq, Sk, R, causal, scale, masked, dtype): head_dim 32 with factor operands
+BWD_FORM_CASES = [
+    (40, 6, 256, 256, 16, False, None, False, torch.bfloat16),    # windowed shape: 480 items of two query tiles
+    (40, 6, 256, 256, 16, False, None, True, torch.bfloat16),     # ... with a shifted-window mask, period 4
+    (2, 40, 1024, 1024, 2, True, None, False, torch.bfloat16),    # causal: items of 8 ... 1 query tiles
+    (3, 50, 200, 1000, 8, True, 0.25, False, torch.float16),      # causal, Sq < Sk: key tiles no query sees; scale 2^-2
+    (5, 31, 130, 257, 24, False, 1.0, False, torch.float16),      # ragged tiles, packed rank 32, scale 1
+    (1, 3, 384, 384, 40, False, None, False, torch.bfloat16),     # fewer items than SMs, packed rank 64
+]
+
+
+@pytest.mark.parametrize("case", BWD_FORM_CASES, ids=lambda c: "B%dH%dSq%dSk%dR%d%s%s" % (c[0], c[1], c[2], c[3], c[4], "c" if c[5] else "", "m" if c[7] else ""))
+def test_backward_persistent_and_one_item_forms_agree(case):
+    B, H, Sq, Sk, R, causal, scale, masked, dtype = case
+    D = 32
+    g = torch.Generator().manual_seed(1234 + Sq + R)
+    q, do = (torch.randn(B, Sq, H, D, generator=g) for _ in range(2))
+    k, v = (torch.randn(B, Sk, H, D, generator=g) for _ in range(2))
+    qb = torch.randn(1, Sq, H, R, generator=g) * 0.5       # shared by the batch: bulk reductions from many CTAs
+    kb = torch.randn(1, Sk, H, R, generator=g) * 0.5
+    mask = None
+    if masked:
+        mask = torch.where(torch.rand(4, 1, Sq, Sk, generator=g) < 0.3, torch.tensor(-100.0), torch.tensor(0.0))
+    host = [t.to(dtype) for t in (q, k, v, qb, kb, do)]
+    scale = scale or 1.0 / math.sqrt(D)
+    tag = "bwdform/B%dH%dSq%dSk%dR%d%s%s" % (B, H, Sq, Sk, R, "c" if causal else "", "m" if masked else "")
+    out = {}
+    for name, flag in (("one_item", _lib.FB_FLAG_BWD_ONE_ITEM), ("persistent", _lib.FB_FLAG_BWD_PERSISTENT)):
+        _check_all(f"{tag}/{name}", host, mask, causal, scale, dtype, flags=flag)
+        dev = [t.cuda() for t in host]
+        mdev = mask.cuda() if mask is not None else None
+        o, lse, sc = flash_bias_forward(dev[0], dev[1], dev[2], dev[3], dev[4], mdev, causal, scale, flags=flag)
+        out[name] = flash_bias_backward(dev[5], dev[0], dev[1], dev[2], o, dev[3], dev[4], lse, mdev, causal, sc,
+                                        flags=flag)
+        torch.cuda.synchronize()
+        check_device_status()
+    # same arithmetic per work item in both forms: dk and dv are bit-identical; dq and the factor gradients are
+    # fp32 sums whose order depends on the schedule
+    assert torch.equal(out["one_item"][1], out["persistent"][1])
+    assert torch.equal(out["one_item"][2], out["persistent"][2])
+    for i in (0, 3, 4):
+        a, b = out["one_item"][i].float(), out["persistent"][i].float()
+        assert (a - b).abs().max().item() <= 2e-2 * max(1.0, a.abs().max().item())
+
+
+# ---------------------------------------------------------------------------------------------------------------
 # operator-level behaviour
 # ---------------------------------------------------------------------------------------------------------------
 def test_expanded_view_factors_get_summed_gradients():
