@@ -62,10 +62,10 @@ bwd_p_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                  sP = sbase + Cfg::OFF_P, sDS = sbase + Cfg::OFF_DS, sStg = sbase + Cfg::OFF_STG,
                  sStgB = sStg + 128 * D * 4;
   const uint32_t bar0 = sbase + Cfg::OFF_BAR;
-  const uint32_t kv_full = bar0, dp_full = bar0 + 16, sdp_read = bar0 + 24,
+  const uint32_t kva_full = bar0, kvb_full = bar0 + 8, dp_full = bar0 + 16, sdp_read = bar0 + 24,
                  dq_full = bar0 + 32 /*2*/, qdo_full = bar0 + 48 /*3*/, qdo_free = bar0 + 72 /*3*/,
                  all_done = bar0 + 112, pds_free = bar0 + 120, pds_ready = bar0 + 136 /*2*/,
-                 dq_drained = bar0 + 152 /*2*/, acc_free = bar0 + 168;
+                 dq_drained = bar0 + 152 /*2*/, acc_free = bar0 + 168, sdp_done = bar0 + 176;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::OFF_BAR + 96);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::OFF_BAR + 104);
 
@@ -110,18 +110,29 @@ bwd_p_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (RP) tma_tile_bwd<RPX>(base + Cfg::OFF_QB, &tmQb, qdo_full + 8 * st, q0, hq, bq);
     tma_tile_bwd<D>(base + Cfg::OFF_DO, &tmDO, qdo_full + 8 * st, q0, x.h, x.b);
   };
-  // producer thread only: the resident tiles of an item's key block
-  auto load_kv = [&](const BwdItem& x) {
+  // The resident tiles of an item's key block, in two groups by reader.  Group A -- (hi, lo) of k*scale, Kb, V --
+  // is read by the S and dP products only: the thread that issues them reloads it for the next item as soon as the
+  // last S|dP of this item has completed, one query tile before the item ends, so that the tensor core computes
+  // the next item's first S and dP under this item's last tile of arithmetic.  Group B -- K, Kc -- is read by
+  // the dQ | dQb products (K also by S when the scale is not split): the producer reloads it after the last dQ.
+  constexpr uint32_t KVA_BYTES = (NQ == 2 ? 2 * Cfg::D_BYTES : 0) + Cfg::R_BYTES + Cfg::D_BYTES;
+  constexpr uint32_t KVB_BYTES = Cfg::D_BYTES + Cfg::RC_BYTES;
+  static_assert(KVA_BYTES + KVB_BYTES == (uint32_t)Cfg::KV_BYTES, "resident tiles");
+  auto load_kva = [&](const BwdItem& x) {
     const int hk = a.hk_bcast ? 0 : x.h, bk = a.bk_bcast ? 0 : x.b;
-    mbar_expect_tx(kv_full, Cfg::KV_BYTES);
-    tma_tile_bwd<D>(sK, &tmK, kv_full, x.k0, x.h, x.b);
+    mbar_expect_tx(kva_full, KVA_BYTES);
     if (NQ == 2) {
-      tma_tile_bwd<D>(sKs, &tmKs, kv_full, x.k0, x.h, x.b);
-      tma_tile_bwd<D>(sKs + Cfg::D_BYTES, &tmKs, kv_full, x.k0, x.h, x.b, D);
+      tma_tile_bwd<D>(sKs, &tmKs, kva_full, x.k0, x.h, x.b);
+      tma_tile_bwd<D>(sKs + Cfg::D_BYTES, &tmKs, kva_full, x.k0, x.h, x.b, D);
     }
-    if (RP) tma_tile_bwd<RPX>(sKb, &tmKb, kv_full, x.k0, hk, bk);
-    tma_tile_bwd<D>(sV, &tmV, kv_full, x.k0, x.h, x.b);
-    if (RP) tma_tile_bwd<Cfg::RCX>(sKc, &tmKc, kv_full, x.k0, hk, bk);
+    if (RP) tma_tile_bwd<RPX>(sKb, &tmKb, kva_full, x.k0, hk, bk);
+    tma_tile_bwd<D>(sV, &tmV, kva_full, x.k0, x.h, x.b);
+  };
+  auto load_kvb = [&](const BwdItem& x) {
+    const int hk = a.hk_bcast ? 0 : x.h, bk = a.bk_bcast ? 0 : x.b;
+    mbar_expect_tx(kvb_full, KVB_BYTES);
+    tma_tile_bwd<D>(sK, &tmK, kvb_full, x.k0, x.h, x.b);
+    if (RP) tma_tile_bwd<Cfg::RCX>(sKc, &tmKc, kvb_full, x.k0, hk, bk);
   };
   // cursor of the ring loads (producer thread): runs NSTAGE tiles ahead of the products, across item boundaries
   int lw = 0, lit = 0;
@@ -141,7 +152,9 @@ bwd_p_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (warp == 12) {
     if (lane == 0) {
       *abort_flag = 0;
-      mbar_init(kv_full, 1);
+      mbar_init(kva_full, 1);
+      mbar_init(kvb_full, 1);
+      mbar_init(sdp_done, 1);  // the last S|dP products of an item have completed
       mbar_init(dp_full, 1);
       mbar_init(sdp_read, 8);  // every compute warp has S and dP of the tile in registers
       mbar_init(all_done, 4);  // one commit per issuing thread, per item
@@ -162,7 +175,8 @@ bwd_p_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       // the first loads start before the rest of the CTA has finished its set-up
       lx = next_active(lw);
       if (lx.valid) {
-        load_kv(lx);
+        load_kva(lx);
+        load_kvb(lx);
         for (int i = 0; i < Cfg::NSTAGE && lx.valid; ++i) load_next();
       }
     }
@@ -222,11 +236,7 @@ bwd_p_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       for (int w = 0;; ++w) {
         const BwdItem x = next_active(w);
         if (!x.valid) break;
-        if (n > 0) {  // every product that reads the resident tiles of the previous item has completed
-          mbar_wait(all_done, (n - 1) & 1, abort_flag, a.status);
-          load_kv(x);
-        }
-        mbar_wait(kv_full, n & 1, abort_flag, a.status);
+        mbar_wait(kvb_full, n & 1, abort_flag, a.status);
 #pragma unroll 1
         for (int it = 0; it < x.n_it; ++it, ++tn) {
           issue_dQ(tn);
@@ -236,6 +246,12 @@ bwd_p_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           }
         }
         umma_commit(all_done);
+        const BwdItem nx = get_item(w + 1, pa.active_items);
+        if (nx.valid) {  // K and Kc are free once the dQ | dQb products of the item's last tile have completed
+          const uint32_t tl = tn - 1;
+          mbar_wait(dq_full + 8 * (tl % Cfg::NDQ), (tl / Cfg::NDQ) & 1, abort_flag, a.status);
+          load_kvb(nx);
+        }
         ++n;
       }
     }
@@ -284,7 +300,8 @@ bwd_p_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         for (int w = 0;; ++w) {
           const BwdItem x = next_active(w);
           if (!x.valid) break;
-          mbar_wait(kv_full, n & 1, abort_flag, a.status);
+          mbar_wait(kva_full, n & 1, abort_flag, a.status);
+          if (NQ != 2) mbar_wait(kvb_full, n & 1, abort_flag, a.status);  // S reads K itself
           tc_fence_after_sync();
 #pragma unroll 1
           for (int it = 0; it < x.n_it; ++it, ++tn) {
@@ -315,10 +332,18 @@ bwd_p_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
               umma_ss(tmem + Cfg::T_DP, desc_at(kDO, so + kmajor_step<D>(s)), desc_at(kV, kmajor_step<D>(s)), idS,
                       s > 0);
             umma_commit(dp_full);
+            if (it + 1 == x.n_it) umma_commit(sdp_done);
             if (Cfg::SEP_DKB) {
               if (it > 0) issue_dKb(it - 1, tn - 1);
             } else {
               umma_commit(qdo_free + 8 * st);
+            }
+          }
+          {
+            const BwdItem nx = get_item(w + 1, pa.active_items);
+            if (nx.valid) {  // group A of the next item, while the compute warps are on this item's last tile
+              mbar_wait(sdp_done, n & 1, abort_flag, a.status);
+              load_kva(nx);
             }
           }
           if (Cfg::SEP_DKB) issue_dKb(x.n_it - 1, tn - 1);
@@ -380,22 +405,36 @@ bwd_p_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const int row = (warp & 3) * 32 + lane;
       const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
       float* s_kbc = reinterpret_cast<float*>(smem + Cfg::OFF_KBC);
+      // k_bias of the four keys the centred copy refers to (one per 32-key group), as fp32, laid out [column][key
+      // group]: one entry per thread, fetched one item ahead so that the load is not waited for at the item's head
+      float kbc_next = 0.f;
+      auto fetch_kbc = [&](const BwdItem& y) {
+        const int i = (int)threadIdx.x - 256;
+        const int c = i >> 2, g = i & 3;
+        kbc_next = 0.f;
+        if (i < 2 * Cfg::RCX && c < a.R) {
+          const T* kb_bh = a.k_bias_t<T>() + (a.bk_bcast ? 0 : y.b) * a.kb_stride[0] + (a.hk_bcast ? 0 : y.h) * a.kb_stride[1];
+          kbc_next = to_f32(kb_bh[(int64_t)min(y.k0 + 32 * g + 16, a.Sk - 1) * a.kb_stride[2] + c]);
+        }
+      };
+      if (RP) {
+        int w0 = 0;
+        const BwdItem first = next_active(w0);
+        if (first.valid) fetch_kbc(first);
+      }
       uint32_t tn = 0;  // running tile count
 #pragma unroll 1
       for (int w = 0;; ++w) {
       const BwdItem x = next_active(w);
       if (!x.valid) break;
-      const int b = x.b, h = x.h, bh = x.bh, i_begin = x.i_begin, k0 = x.k0;
+      const int b = x.b, h = x.h, bh = x.bh, i_begin = x.i_begin;
       if (RP) {
-        // k_bias of the four keys the centred copy refers to (one per 32-key group), as fp32.  Written and read by
-        // this warpgroup only: every tile of the previous item has been drained when it gets here.
+        // written and read by this warpgroup only: every tile of the previous item has been drained when it gets here
         asm volatile("bar.sync 3, 128;" ::: "memory");
-        const T* kb_bh = a.k_bias_t<T>() + (a.bk_bcast ? 0 : b) * a.kb_stride[0] + (a.hk_bcast ? 0 : h) * a.kb_stride[1];
-        for (int i = threadIdx.x - 256; i < 4 * Cfg::RCX; i += 128) {
-          const int g = i / Cfg::RCX, c = i % Cfg::RCX;
-          s_kbc[i] = c < a.R ? to_f32(kb_bh[(int64_t)min(k0 + 32 * g + 16, a.Sk - 1) * a.kb_stride[2] + c]) : 0.f;
-        }
+        if ((int)threadIdx.x - 256 < 2 * Cfg::RCX) s_kbc[threadIdx.x - 256] = kbc_next;
         asm volatile("bar.sync 3, 128;" ::: "memory");
+        const BwdItem nx = get_item(w + 1, pa.active_items);
+        if (nx.valid) fetch_kbc(nx);
       }
 #pragma unroll 1
       for (int it = 0; it < x.n_it; ++it, ++tn) {
@@ -422,14 +461,21 @@ bwd_p_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         } else {
           // dQ tile: TMEM -> registers -> shared-memory staging -> ONE bulk reduction into the fp32 accumulator.
           // Per-thread vector reductions (32 per row) crowd the load/store unit that the compute warps need for
-          // their P/dS stores; the bulk form is executed by the copy engine.
-          // the thread that issued the previous tile's reduction has seen its shared-memory reads complete
+          // their P/dS stores; the bulk form is executed by the copy engine.  The first columns are fetched into
+          // registers while the copy engine may still be reading the previous tile from the staging tile; the
+          // thread that issued that reduction then waits for its shared-memory reads and the warpgroup syncs.
+          uint32_t r0[16], r1[16];
+          tmem_ld16(tq + Cfg::T_DQ, r0);
+          tmem_ld16(tq + Cfg::T_DQ + 16, r1);
+          if (warp == 8 && lane == 0) bulk_wait_group_read0();
+          __syncwarp();
           asm volatile("bar.sync 3, 128;" ::: "memory");  // the drain warpgroup only
 #pragma unroll 1
           for (int c0 = 0; c0 < D; c0 += 32) {
-            uint32_t r0[16], r1[16];
-            tmem_ld16(tq + Cfg::T_DQ + c0, r0);
-            tmem_ld16(tq + Cfg::T_DQ + c0 + 16, r1);
+            if (c0 > 0) {
+              tmem_ld16(tq + Cfg::T_DQ + c0, r0);
+              tmem_ld16(tq + Cfg::T_DQ + c0 + 16, r1);
+            }
             tmem_wait_ld(r0);
             tmem_wait_ld(r1);
 #pragma unroll
@@ -442,40 +488,13 @@ bwd_p_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           }
         }
         if (RP) {
-          // dq_bias = dS . k_bias, evaluated per group of 32 keys as dS16 . (k_bias - c) + c * rowsum_fp32(dS)
-          // with c the k_bias of the group's middle key: rows of dS sum to ~0, so rounding dS to 16 bits
-          // against a large, slowly varying factor (ALiBi positions) would otherwise dominate the result.
           const float* s_rowsum = reinterpret_cast<const float*>(smem + Cfg::OFF_ROWSUM) + (tn & 3) * 512;
-          float rsum[4];
-#pragma unroll
-          for (int g = 0; g < 4; ++g) rsum[g] = s_rowsum[g * 128 + row];
           const int bq = a.bq_bcast ? 0 : b, hq = a.hq_bcast ? 0 : h;
-          // accumulator laid out (Bq, Hq, query tiles, R, 128 rows): a tile is contiguous and stored rank-major, so
-          // that the threads of a warp (consecutive rows) write consecutive floats of the staging tile
+          // accumulator laid out (Bq, Hq, query tiles, R, 128 rows): a tile is contiguous
           float* tileb = a.dqb_acc + (bh % a.dqb_slots) * a.dqb_slot_stride +
                          (((int64_t)bq * a.Hq + hq) * a.nq_tiles + (i_begin + it)) * (128 * a.R);
           float* stgb = reinterpret_cast<float*>(smem + Cfg::OFF_STG + 128 * D * 4) + row;
-          const int used = 2 * a.R;  // (hi, lo) column groups of the centred factor
-#pragma unroll 1
-          for (int c0 = 0; c0 < Cfg::RCX && c0 < used; c0 += 16) {
-            uint32_t r[16];
-            tmem_ld16(tq + Cfg::T_DQB + c0, r);
-            tmem_wait_ld(r);
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const int c = c0 + i;
-              if (c < a.R) {
-                float v = __uint_as_float(r[i]);
-#pragma unroll
-                for (int g = 0; g < 4; ++g) v = fmaf(s_kbc[g * Cfg::RCX + c], rsum[g], v);
-                if (Cfg::STAGED) stgb[c * 128] = v;
-                else if (grow < a.Sq) atomicAdd(tileb + c * 128 + row, v);
-              } else if (c < used) {
-                if (Cfg::STAGED) stgb[(c - a.R) * 128] += __uint_as_float(r[i]);
-                else if (grow < a.Sq) atomicAdd(tileb + (c - a.R) * 128 + row, __uint_as_float(r[i]));
-              }
-            }
-          }
+          drain_dq_bias<Cfg>(tq + Cfg::T_DQB, s_rowsum, sbase + Cfg::OFF_KBC, stgb, tileb, row, grow < a.Sq, a.R);
         }
         tc_fence_before_sync();
         mbar_arrive_warp(dq_drained + 8 * qb);  // every tensor-memory read of the tile is done
@@ -494,12 +513,12 @@ bwd_p_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                   128 * a.R * 4);
             }
             bulk_commit_group();
-            bulk_wait_group_read0();
           }
         }
       }
       }
-      // (the last reduction's shared-memory reads were awaited above; its global side completes with the kernel)
+      // the staging tile must outlive the last reduction's reads; its global side completes with the kernel
+      if (Cfg::STAGED && warp == 8 && lane == 0) bulk_wait_group_read0();
     }
   } else {
     // ------------------------------------------------------------------ compute warpgroups (warps 0-7)

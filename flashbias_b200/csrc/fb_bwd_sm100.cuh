@@ -162,6 +162,45 @@ __host__ __device__ __forceinline__ int dq_stage_off(int r, int ch) {
   return (ch >> 3) * (128 * 128) + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
 }
 
+// dq_bias of one query tile, one thread per query row: dq_bias = dS . k_bias, evaluated per group of 32 keys as
+// dS16 . (k_bias - c) + c * rowsum_fp32(dS) with c the k_bias of the group's middle key (rows of dS sum to ~0, so
+// rounding dS to 16 bits against a large, slowly varying factor -- ALiBi positions -- would otherwise dominate the
+// result).  The accumulator holds dS16 . hi(k_bias - c) in columns [0, R) and dS16 . lo(k_bias - c) in columns
+// [RCX/2, RCX/2 + R); s_kbc holds c as [column][key group] (4 floats per column, one vector load).
+// The result goes rank-major ([R][128 rows]) into the staging tile (STAGED) or straight into the accumulator in
+// global memory: consecutive threads then write consecutive floats.
+template <typename Cfg>
+__device__ __forceinline__ void drain_dq_bias(uint32_t tq_dqb, const float* s_rowsum, uint32_t s_kbc, float* stgb,
+                                              float* tileb, int row, bool row_ok, int R) {
+  constexpr int HALF = Cfg::RCX / 2;
+  constexpr int W = HALF >= 16 ? 16 : 8;
+  float rsum[4];
+#pragma unroll
+  for (int g = 0; g < 4; ++g) rsum[g] = s_rowsum[g * 128 + row];
+#pragma unroll 1
+  for (int c0 = 0; c0 < HALF && c0 < R; c0 += W) {
+    uint32_t rh[W], rl[W];
+    tmem_ld(tq_dqb + c0, rh);
+    tmem_ld(tq_dqb + HALF + c0, rl);
+    tmem_wait_ld(rh);
+    tmem_wait_ld(rl);
+#pragma unroll
+    for (int i = 0; i < W; ++i) {
+      const int c = c0 + i;
+      if (c < R) {
+        const float4 kc = ld_shared_v4f(s_kbc + c * 16);
+        float v = __uint_as_float(rh[i]) + __uint_as_float(rl[i]);
+        v = fmaf(kc.x, rsum[0], v);
+        v = fmaf(kc.y, rsum[1], v);
+        v = fmaf(kc.z, rsum[2], v);
+        v = fmaf(kc.w, rsum[3], v);
+        if (Cfg::STAGED) stgb[c * 128] = v;
+        else if (row_ok) atomicAdd(tileb + c * 128 + row, v);
+      }
+    }
+  }
+}
+
 enum { BWD_PLAIN = 0, BWD_MASK = 1, BWD_ALIBI = 2 };
 
 // MODE: how the logits are completed -- as computed (BWD_PLAIN), plus an additive mask tensor (BWD_MASK), plus the
@@ -439,7 +478,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (n_it > 0) {
       const int row = (warp & 3) * 32 + lane;
       const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
-      const float* s_kbc = reinterpret_cast<const float*>(smem + Cfg::OFF_KBC);
 #pragma unroll 1
       for (int it = 0; it < n_it; ++it) {
         const int grow = (i_begin + it) * 128 + row;
@@ -465,14 +503,21 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         } else {
           // dQ tile: TMEM -> registers -> shared-memory staging -> ONE bulk reduction into the fp32 accumulator.
           // Per-thread vector reductions (32 per row) crowd the load/store unit that the compute warps need for
-          // their P/dS stores; the bulk form is executed by the copy engine.
-          // the thread that issued the previous tile's reduction has seen its shared-memory reads complete
+          // their P/dS stores; the bulk form is executed by the copy engine.  The first columns are fetched into
+          // registers while the copy engine may still be reading the previous tile from the staging tile; the
+          // thread that issued that reduction then waits for its shared-memory reads and the warpgroup syncs.
+          uint32_t r0[16], r1[16];
+          tmem_ld16(tq + Cfg::T_DQ, r0);
+          tmem_ld16(tq + Cfg::T_DQ + 16, r1);
+          if (warp == 8 && lane == 0) bulk_wait_group_read0();
+          __syncwarp();
           asm volatile("bar.sync 3, 128;" ::: "memory");  // the drain warpgroup only
 #pragma unroll 1
           for (int c0 = 0; c0 < D; c0 += 32) {
-            uint32_t r0[16], r1[16];
-            tmem_ld16(tq + Cfg::T_DQ + c0, r0);
-            tmem_ld16(tq + Cfg::T_DQ + c0 + 16, r1);
+            if (c0 > 0) {
+              tmem_ld16(tq + Cfg::T_DQ + c0, r0);
+              tmem_ld16(tq + Cfg::T_DQ + c0 + 16, r1);
+            }
             tmem_wait_ld(r0);
             tmem_wait_ld(r1);
 #pragma unroll
@@ -485,40 +530,13 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
         }
         if (RP) {
-          // dq_bias = dS . k_bias, evaluated per group of 32 keys as dS16 . (k_bias - c) + c * rowsum_fp32(dS)
-          // with c the k_bias of the group's middle key: rows of dS sum to ~0, so rounding dS to 16 bits
-          // against a large, slowly varying factor (ALiBi positions) would otherwise dominate the result.
           const float* s_rowsum = reinterpret_cast<const float*>(smem + Cfg::OFF_ROWSUM) + (it & 3) * 512;
-          float rsum[4];
-#pragma unroll
-          for (int g = 0; g < 4; ++g) rsum[g] = s_rowsum[g * 128 + row];
           const int bq = a.bq_bcast ? 0 : b, hq = a.hq_bcast ? 0 : h;
-          // accumulator laid out (Bq, Hq, query tiles, R, 128 rows): a tile is contiguous and stored rank-major, so
-          // that the threads of a warp (consecutive rows) write consecutive floats of the staging tile
+          // accumulator laid out (Bq, Hq, query tiles, R, 128 rows): a tile is contiguous
           float* tileb = a.dqb_acc + (bh % a.dqb_slots) * a.dqb_slot_stride +
                          (((int64_t)bq * a.Hq + hq) * a.nq_tiles + (i_begin + it)) * (128 * a.R);
           float* stgb = reinterpret_cast<float*>(smem + Cfg::OFF_STG + 128 * D * 4) + row;
-          const int used = 2 * a.R;  // (hi, lo) column groups of the centred factor
-#pragma unroll 1
-          for (int c0 = 0; c0 < Cfg::RCX && c0 < used; c0 += 16) {
-            uint32_t r[16];
-            tmem_ld16(tq + Cfg::T_DQB + c0, r);
-            tmem_wait_ld(r);
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const int c = c0 + i;
-              if (c < a.R) {
-                float v = __uint_as_float(r[i]);
-#pragma unroll
-                for (int g = 0; g < 4; ++g) v = fmaf(s_kbc[g * Cfg::RCX + c], rsum[g], v);
-                if (Cfg::STAGED) stgb[c * 128] = v;
-                else if (grow < a.Sq) atomicAdd(tileb + c * 128 + row, v);
-              } else if (c < used) {
-                if (Cfg::STAGED) stgb[(c - a.R) * 128] += __uint_as_float(r[i]);
-                else if (grow < a.Sq) atomicAdd(tileb + (c - a.R) * 128 + row, __uint_as_float(r[i]));
-              }
-            }
-          }
+          drain_dq_bias<Cfg>(tq + Cfg::T_DQB, s_rowsum, sbase + Cfg::OFF_KBC, stgb, tileb, row, grow < a.Sq, a.R);
         }
         tc_fence_before_sync();
         mbar_arrive_warp(dq_drained + 8 * qb);  // every tensor-memory read of the tile is done
@@ -537,11 +555,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                   128 * a.R * 4);
             }
             bulk_commit_group();
-            bulk_wait_group_read0();
           }
         }
       }
-      // (the last reduction's shared-memory reads were awaited above; its global side completes with the kernel)
+      // the staging tile must outlive the last reduction's reads; its global side completes with the kernel
+      if (Cfg::STAGED && warp == 8 && lane == 0) bulk_wait_group_read0();
     }
   } else if (n_it > 0) {
     // ------------------------------------------------------------------ compute warpgroups (warps 0-7)
@@ -556,8 +574,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       // k_bias of the four keys the centred copy refers to (one per 32-key group), as fp32; read by the drain
       // warpgroup, which is ordered after this through the first pds_ready -> dq_full chain
       const T* kb_bh = a.k_bias_t<T>() + (a.bk_bcast ? 0 : b) * a.kb_stride[0] + (a.hk_bcast ? 0 : h) * a.kb_stride[1];
-      for (int i = threadIdx.x; i < 4 * Cfg::RCX; i += 256) {
-        const int g = i / Cfg::RCX, c = i % Cfg::RCX;
+      for (int i = threadIdx.x; i < 2 * Cfg::RCX; i += 256) {  // [column][key group]
+        const int c = i >> 2, g = i & 3;
         s_kbc[i] = c < a.R ? to_f32(kb_bh[(int64_t)min(k0 + 32 * g + 16, a.Sk - 1) * a.kb_stride[2] + c]) : 0.f;
       }
     }

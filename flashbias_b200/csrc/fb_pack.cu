@@ -115,7 +115,7 @@ __device__ __forceinline__ void pack_factor_row(const FactorJob<T>& j, int64_t i
   if (dst_centered) {
     // k-side factor minus the factor of the middle key of its group of 32 keys: small-magnitude copy used
     // for dq_bias = dS.k_bias (the removed constant is re-applied in fp32 through the row sum of dS);
-    // two-term split: columns [0,R) hi, [R,2R) lo, zero beyond
+    // two-term split: columns [0,R) hi, [RC/2, RC/2 + R) lo, zero elsewhere
     int s0 = (s & ~31) + 16;
     if (s0 > S - 1) s0 = S - 1;
     const T* in0 = src + b * sb + h * sh + (int64_t)s0 * ss;
@@ -125,11 +125,12 @@ __device__ __forceinline__ void pack_factor_row(const FactorJob<T>& j, int64_t i
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int c = c0 + i;
-        if (c < 2 * R) {
-          const int cc = c < R ? c : c - R;
+        const bool lo = c >= RC / 2;
+        const int cc = lo ? c - RC / 2 : c;
+        if (cc < R) {
           const float x = to_f32(in[cc]) - to_f32(in0[cc]);
           const T hi = from_f32<T>(x);
-          y[i] = c < R ? hi : from_f32<T>(x - to_f32(hi));
+          y[i] = lo ? from_f32<T>(x - to_f32(hi)) : hi;
         }
       }
       *reinterpret_cast<uint4*>(dst_centered + idx * RC + c0) = w;
