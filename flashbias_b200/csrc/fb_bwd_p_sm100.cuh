@@ -48,6 +48,7 @@ bwd_p_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                  const __grid_constant__ CUtensorMap tmQb, const __grid_constant__ CUtensorMap tmKb,
                  const __grid_constant__ CUtensorMap tmKc, const __grid_constant__ CUtensorMap tmKs,
+                 const __grid_constant__ CUtensorMap tmDK, const __grid_constant__ CUtensorMap tmDV,
                  const BwdArgs a, const BwdPArgs pa) {
   using Cfg = BwdCfg<D, RP, NQ>;
   constexpr int RPX = Cfg::RPX;
@@ -530,6 +531,19 @@ bwd_p_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     constexpr int DH = D / 2;  // dV / dK columns per warpgroup in the epilogue
     uint32_t tn = 0;  // running tile count
     int n = 0;        // items with work so far
+    // Row statistics of a query tile.  Raw loads only: the values are consumed one tile later, so the global-memory
+    // latency hides under the current tile's math instead of stalling the thread (volatile: the compiler must not
+    // sink the loads to their use).
+    auto load_stats = [&](int bh_, int g, bool ok, float& lse_raw, float& dlt) {
+      lse_raw = INFINITY;
+      dlt = 0.f;
+      if (ok && g < a.Sq) {
+        asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(lse_raw) : "l"(a.lse + (int64_t)bh_ * a.lse_stride_bh + g));
+        asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(dlt) : "l"(a.delta + (int64_t)bh_ * a.lse_stride_bh + g));
+      }
+    };
+    float lse_raw = INFINITY, dlt = 0.f;
+    bool staged_out = false;  // an item's epilogue tiles may still be being read from the P tile
 #pragma unroll 1
     for (int w = 0;; ++w) {
     const BwdItem x = get_item(w, pa.total_items);
@@ -550,21 +564,7 @@ bwd_p_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       continue;
     }
 
-    // Raw loads only: the values are consumed one iteration later, so the global-memory latency
-    // hides under the current tile's math instead of stalling the thread here.
-    auto load_row_stats = [&](int it, float& lse_raw, float& dlt) {
-      const int g = (i_begin + it) * 128 + row;
-      lse_raw = INFINITY;
-      dlt = 0.f;
-      if (it < n_it && g < a.Sq) {
-        // volatile: the compiler must not sink the loads to their use one tile later
-        asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(lse_raw) : "l"(a.lse + (int64_t)bh * a.lse_stride_bh + g));
-        asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(dlt) : "l"(a.delta + (int64_t)bh * a.lse_stride_bh + g));
-      }
-    };
-
-    float lse_raw, dlt;
-    load_row_stats(0, lse_raw, dlt);
+    if (n == 0) load_stats(bh, i_begin * 128 + row, true, lse_raw, dlt);  // later items: fetched in the previous item's last tile
     float slope2 = 0.f;  // ALiBi slope of this head, times log2 e
     if (MODE == BWD_ALIBI) slope2 = __ldg(a.alibi_slopes + h) * kLog2e;
     const char* mrow = nullptr;  // additive mask of this (batch, head), row 0
@@ -653,7 +653,13 @@ bwd_p_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       };
       uint32_t pk0[16], pk1[16], dk0[16], dk1[16];
       ds_sum0 = chunk(rs0, rd0, pk0, dk0, 0);
-      load_row_stats(it + 1, lse_raw, dlt);  // next tile's statistics: the loads complete under this tile's math
+      // next tile's statistics (the next item's first tile after the last one): the loads complete under this math
+      if (it + 1 < n_it) {
+        load_stats(bh, (i_begin + it + 1) * 128 + row, true, lse_raw, dlt);
+      } else {
+        const BwdItem nx = get_item(w + 1, pa.active_items);
+        load_stats(nx.bh, nx.i_begin * 128 + row, nx.valid, lse_raw, dlt);
+      }
       ds_sum1 = chunk(rs1, rd1, pk1, dk1, 1);
       // Chunk 0 of the next tile is fetched under the stores below if its S and dP are already there (they were
       // issued when this tile was released).  If not -- a 2-stage ring delivers the next tile late -- the stores
@@ -670,6 +676,11 @@ bwd_p_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       // the dV, dK and dQ products of the query tile that used this buffer pair last have read P and dS
       if (tn >= (uint32_t)Cfg::NBUF)
         mbar_wait(pds_free + 8 * (tn % Cfg::NBUF), (tn / Cfg::NBUF - 1) & 1, abort_flag, a.status);
+      if (it == 0 && staged_out) {  // the previous item's epilogue tiles have left the P tile
+        if (threadIdx.x == 0) bulk_wait_group_read0();
+        __syncwarp();
+        asm volatile("bar.sync 5, 256;" ::: "memory");
+      }
       const uint32_t pb = (tn % Cfg::NBUF) * Cfg::PDS_STRIDE;
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
@@ -700,11 +711,12 @@ bwd_p_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_wait(all_done, n & 1, abort_flag, a.status);
     tc_fence_after_sync();
 
-    // ---- epilogue: dV, dK (x scale), dKb
-    const int krow = k0 + row;
+    // ---- epilogue: dV, dK (x scale), dKb.  The tiles are staged in the (now idle) P tile -- dV, dK as the 16-bit
+    // [128][D] tiles a TMA store takes, dk_bias rank-major as fp32 -- and leave through the copy engine: one tile
+    // store each for dV and dK (whole rows; per-thread stores would touch 32 lines per instruction) and one bulk
+    // reduction for dk_bias (other (batch, head) pairs add to the same rows when the factor is shared).
+    static_assert(2 * Cfg::D_BYTES + 128 * (RPX / 2) * 4 <= Cfg::TILE128 || !RP, "epilogue staging");
     {
-      T* dvrow = reinterpret_cast<T*>(a.dv) + b * a.dv_stride[0] + h * a.dv_stride[1] + (int64_t)krow * a.dv_stride[2];
-      T* dkrow = reinterpret_cast<T*>(a.dk) + b * a.dk_stride[0] + h * a.dk_stride[1] + (int64_t)krow * a.dk_stride[2];
 #pragma unroll 1
       for (int c0 = wg * DH; c0 < wg * DH + DH; c0 += 16) {
         uint32_t rv[16], rk[16];
@@ -712,29 +724,23 @@ bwd_p_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tmem_ld16(tmem + Cfg::T_DK + lane_off + c0, rk);
         tmem_wait_ld(rv);
         tmem_wait_ld(rk);
-        if (krow < a.Sk) {
 #pragma unroll
-          for (int g = 0; g < 2; ++g) {
-            uint4 wv, wk;
-            wv.x = Pack2<T>::pack(__uint_as_float(rv[g * 8 + 0]), __uint_as_float(rv[g * 8 + 1]));
-            wv.y = Pack2<T>::pack(__uint_as_float(rv[g * 8 + 2]), __uint_as_float(rv[g * 8 + 3]));
-            wv.z = Pack2<T>::pack(__uint_as_float(rv[g * 8 + 4]), __uint_as_float(rv[g * 8 + 5]));
-            wv.w = Pack2<T>::pack(__uint_as_float(rv[g * 8 + 6]), __uint_as_float(rv[g * 8 + 7]));
-            wk.x = Pack2<T>::pack(__uint_as_float(rk[g * 8 + 0]) * a.dk_scale, __uint_as_float(rk[g * 8 + 1]) * a.dk_scale);
-            wk.y = Pack2<T>::pack(__uint_as_float(rk[g * 8 + 2]) * a.dk_scale, __uint_as_float(rk[g * 8 + 3]) * a.dk_scale);
-            wk.z = Pack2<T>::pack(__uint_as_float(rk[g * 8 + 4]) * a.dk_scale, __uint_as_float(rk[g * 8 + 5]) * a.dk_scale);
-            wk.w = Pack2<T>::pack(__uint_as_float(rk[g * 8 + 6]) * a.dk_scale, __uint_as_float(rk[g * 8 + 7]) * a.dk_scale);
-            *reinterpret_cast<uint4*>(dvrow + c0 + g * 8) = wv;
-            *reinterpret_cast<uint4*>(dkrow + c0 + g * 8) = wk;
-          }
+        for (int g = 0; g < 2; ++g) {
+          const uint32_t off = tile_chunk_offset<D>(row, c0 + g * 8);
+          st_shared_v4(sP + off, Pack2<T>::pack(__uint_as_float(rv[g * 8 + 0]), __uint_as_float(rv[g * 8 + 1])),
+                       Pack2<T>::pack(__uint_as_float(rv[g * 8 + 2]), __uint_as_float(rv[g * 8 + 3])),
+                       Pack2<T>::pack(__uint_as_float(rv[g * 8 + 4]), __uint_as_float(rv[g * 8 + 5])),
+                       Pack2<T>::pack(__uint_as_float(rv[g * 8 + 6]), __uint_as_float(rv[g * 8 + 7])));
+          st_shared_v4(sP + Cfg::D_BYTES + off,
+                       Pack2<T>::pack(__uint_as_float(rk[g * 8 + 0]) * a.dk_scale, __uint_as_float(rk[g * 8 + 1]) * a.dk_scale),
+                       Pack2<T>::pack(__uint_as_float(rk[g * 8 + 2]) * a.dk_scale, __uint_as_float(rk[g * 8 + 3]) * a.dk_scale),
+                       Pack2<T>::pack(__uint_as_float(rk[g * 8 + 4]) * a.dk_scale, __uint_as_float(rk[g * 8 + 5]) * a.dk_scale),
+                       Pack2<T>::pack(__uint_as_float(rk[g * 8 + 6]) * a.dk_scale, __uint_as_float(rk[g * 8 + 7]) * a.dk_scale));
         }
       }
     }
     if (RP && wg == 0) {
-      // dk_bias tile of this item: staged rank-major, [R][128], in the (now idle) P tile, one bulk reduction into the
-      // accumulator (other (batch, head) pairs add to the same rows when the factor is shared)
-      const int bk = a.bk_bcast ? 0 : b, hk = a.hk_bcast ? 0 : h;
-      float* stg = reinterpret_cast<float*>(smem + Cfg::OFF_P) + row;
+      float* stg = reinterpret_cast<float*>(smem + Cfg::OFF_P + 2 * Cfg::D_BYTES) + row;
       const int used = a.R;
 #pragma unroll 1
       for (int c0 = 0; c0 < RPX && c0 < used; c0 += 16) {
@@ -745,23 +751,29 @@ bwd_p_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         for (int i = 0; i < 16; ++i)
           if (c0 + i < used) stg[(c0 + i) * 128] = __uint_as_float(r[i]) * a.dkb_scale;
       }
-      fence_proxy_async_smem();
-      asm volatile("bar.sync 4, 128;" ::: "memory");  // warpgroup 0 only
-      if (threadIdx.x == 0) {
-        bulk_reduce_add_f32(a.dkb_acc + (bh % a.dkb_slots) * a.dkb_slot_stride +
-                                (((int64_t)bk * a.Hk + hk) * a.nk_tiles + kt) * (128 * a.R),
-                            sP, 128 * a.R * 4);
-        bulk_commit_group();
-        bulk_wait_group_read0();  // shared memory must stay until it is read; the global side completes with the kernel
-      }
     }
     // the accumulators may be overwritten by the next item's products
     tc_fence_before_sync();
     mbar_arrive_warp(acc_free);
-    // the staged dk_bias tile has been read: the P tile may take the next item's stores (both warpgroups write it)
-    if (RP) asm volatile("bar.sync 5, 256;" ::: "memory");
+    fence_proxy_async_smem();  // the staged tiles become visible to the copy engine
+    asm volatile("bar.sync 5, 256;" ::: "memory");  // both compute warpgroups
+    if (threadIdx.x == 0) {
+      tma_store_4d(&tmDV, sP, 0, k0, h, b);
+      tma_store_4d(&tmDK, sP + Cfg::D_BYTES, 0, k0, h, b);
+      if (RP) {
+        const int bk = a.bk_bcast ? 0 : b, hk = a.hk_bcast ? 0 : h;
+        bulk_reduce_add_f32(a.dkb_acc + (bh % a.dkb_slots) * a.dkb_slot_stride +
+                                (((int64_t)bk * a.Hk + hk) * a.nk_tiles + kt) * (128 * a.R),
+                            sP + 2 * Cfg::D_BYTES, 128 * a.R * 4);
+      }
+      bulk_commit_group();
+      // (the reads of the staged tiles are awaited before the next stores into the P tile, or at the end)
+    }
+    staged_out = true;
     ++n;
     }
+    // the staged tiles must outlive the copy engine's reads; the global side completes with the kernel
+    if (staged_out && threadIdx.x == 0) bulk_wait_group_read0();
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -789,6 +801,11 @@ int launch_bwd_p(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
     fast_div_magic(p->B * p->H, pa.div_bh);
     fast_div_magic(a.nk_tiles, pa.div_nk);
     fast_div_magic(p->H, pa.div_h);
+    CUtensorMap tDK, tDV;  // dK and dV leave through tile stores
+    if ((rc = make_tmap_4d(&tDK, p->dk, D, p->Sk, p->H, p->B, p->dk_stride[2], p->dk_stride[1], p->dk_stride[0], D, 128)))
+      return rc;
+    if ((rc = make_tmap_4d(&tDV, p->dv, D, p->Sk, p->H, p->B, p->dv_stride[2], p->dv_stride[1], p->dv_stride[0], D, 128)))
+      return rc;
     auto kern = bwd_p_sm100_kernel<T, D, RP, NQ, MODE>;
     // per kernel instantiation and device: raise the dynamic shared-memory limit once
     static std::mutex mu;
@@ -808,7 +825,7 @@ int launch_bwd_p(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
     // one CTA per SM (or fewer, if there are fewer work items)
     const unsigned grid = (unsigned)(pa.total_items < sms ? pa.total_items : sms);
     prof_before(KC_BWD_MAIN, st);
-    kern<<<grid, 512, Cfg::SMEM, st>>>(L.tQ, L.tK, L.tV, L.tDO, L.tQb, L.tKb, L.tKc, L.tKs, a, pa);
+    kern<<<grid, 512, Cfg::SMEM, st>>>(L.tQ, L.tK, L.tV, L.tDO, L.tQb, L.tKb, L.tKc, L.tKs, tDK, tDV, a, pa);
     prof_after(KC_BWD_MAIN, st);
     note_launch();
     if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;

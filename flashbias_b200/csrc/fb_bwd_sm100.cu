@@ -54,8 +54,11 @@ static bool bwd_prefers_persistent(const fb_params* p) {
 }
 
 int launch_bwd_sm100(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
+  // (the persistent form writes dK and dV with tile stores: their layout must be one a tensor map can describe)
   if (p->D == 32 && plan.RP > 0 && !p->alibi_slopes && !(p->flags & FB_FLAG_BWD_ONE_ITEM) &&
-      ((p->flags & FB_FLAG_BWD_PERSISTENT) || bwd_prefers_persistent(p)))
+      ((p->flags & FB_FLAG_BWD_PERSISTENT) || bwd_prefers_persistent(p)) &&
+      tma_compatible(p->dk, p->dk_stride[2], p->dk_stride[1], p->dk_stride[0], p->H, p->B) &&
+      tma_compatible(p->dv, p->dv_stride[2], p->dv_stride[1], p->dv_stride[0], p->H, p->B))
     return dispatch_bwd_d32p(p, plan, st);
   return p->D == 32 ? dispatch_bwd_d32(p, plan, st) : p->D == 64 ? dispatch_bwd_d64(p, plan, st) : FB_ENOTBUILT;
 }
