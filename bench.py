@@ -520,6 +520,7 @@ def main():
         frac_r0 = sum((s[1] - s[0]) * (s[3] - s[2]) for s in slabs) / (B * H)
         nfac = (w.q_bias.numel() + w.k_bias.numel()) if w.q_bias is not None else 0
         tensor, hbm, hbm_binds = rooflines(peaks, fl_b * frac_r0, bwd_bytes(sh, nfac) * frac_r0, bwd_kernel_ms)
+        # (bwd_sm100_kernel; its persistent form bwd_p_sm100_kernel where a work item has few query tiles)
         roof = {"bound": "hbm" if hbm_binds else "tensor", "kernel": "bwd_sm100_kernel",
                 **((hbm if hbm_binds else tensor) or {}), "peak_source": peaks["source"],
                 "ms_per_step_in_kernel": bwd_kernel_ms, "launches_timed": kn, "flop_per_step": fl_b * frac_r0,
@@ -566,6 +567,8 @@ def main():
                     flash_bias_alibi_func(pq, pk, pv, sl, True, w.softmax_scale)
 
                 def p_step():
+                    for t in (pq, pk, pv):
+                        t.grad = None
                     flash_bias_alibi_func(pq, pk, pv, sl, True, w.softmax_scale).backward(d0["do"])
 
                 line["detail"]["alibi_producer"] = sub_record(timer, p_fwd, p_step, fl_f, fl_b,

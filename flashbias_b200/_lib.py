@@ -79,6 +79,8 @@ _lib = None
 def load() -> C.CDLL:
     """Load the shared library once; raise if it has not been built."""
     global _lib
+    if _lib is not None:
+        return _lib
     with _lock:
         if _lib is None:
             if not os.path.exists(LIB_PATH):

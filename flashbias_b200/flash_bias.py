@@ -27,24 +27,30 @@ _DT = {torch.float16: _lib.FB_DTYPE_F16, torch.bfloat16: _lib.FB_DTYPE_BF16, tor
 
 
 def _strides_bhs(t: torch.Tensor):
-    """(batch, head, row) element strides of a (B, S, H, C) tensor."""
-    return _lib.I64x3(t.stride(0), t.stride(2), t.stride(1))
+    """(batch, head, row) element strides of a (B, S, H, C) tensor (a tuple: ctypes converts it on assignment)."""
+    sb, ss, sh, _ = t.stride()
+    return (sb, sh, ss)
 
 
 def _factor_strides(t: torch.Tensor):
     """As above with 0 for broadcast (size-1) batch/head dims."""
-    return _lib.I64x3(0 if t.shape[0] == 1 else t.stride(0), 0 if t.shape[2] == 1 else t.stride(2), t.stride(1))
+    sb, ss, sh, _ = t.stride()
+    return (0 if t.shape[0] == 1 else sb, 0 if t.shape[2] == 1 else sh, ss)
 
 
 _status = None
+_status_ptr = 0        # address of the status word
+_status_view = None    # ctypes view of it: reading a host word must not cost a tensor operation per call
 
 
 def _status_word() -> torch.Tensor:
     """One int32 in pinned (device-visible) host memory: kernels store a device-side error code there, the host
     reads it without synchronising anything."""
-    global _status
+    global _status, _status_ptr, _status_view
     if _status is None:
         _status = torch.zeros(1, dtype=torch.int32).pin_memory()
+        _status_ptr = _status.data_ptr()
+        _status_view = C.c_int32.from_address(_status_ptr)
     return _status
 
 
@@ -54,7 +60,7 @@ def check_device_status() -> None:
     forward and backward; callers can also call it after a synchronisation point of their own."""
     if _status is None:
         return
-    code = int(_status[0])
+    code = _status_view.value
     if code != 0:
         _status.zero_()
         raise RuntimeError(f"flashbias_b200: device-side error {code}: "
@@ -73,7 +79,9 @@ def _fill_common(p: _lib.FbParams, q, k, v, q_bias, k_bias, mask, causal, softma
     p.causal = 1 if causal else 0
     p.flags = flags
     p.softmax_scale = softmax_scale
-    p.status = _status_word().data_ptr()
+    if _status is None:
+        _status_word()
+    p.status = _status_ptr
     if alibi_slopes is not None:
         p.alibi_slopes = alibi_slopes.data_ptr()
     p.q, p.k, p.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
@@ -86,9 +94,9 @@ def _fill_common(p: _lib.FbParams, q, k, v, q_bias, k_bias, mask, causal, softma
         p.mask_dtype = _DT[mask.dtype]
         # (1, seqlen_k) is tested first, as in the reference (:1120-1123)
         p.mask_kind = _lib.FB_MASK_VECTOR if mask.shape[2] == 1 else _lib.FB_MASK_MATRIX
-        p.mask_stride = _lib.I64x3(0 if mask.shape[0] == 1 else mask.stride(0),
-                                   0 if mask.shape[1] == 1 else mask.stride(1),
-                                   0 if mask.shape[2] == 1 else mask.stride(2))
+        p.mask_stride = (0 if mask.shape[0] == 1 else mask.stride(0),
+                         0 if mask.shape[1] == 1 else mask.stride(1),
+                         0 if mask.shape[2] == 1 else mask.stride(2))
         # a mask with fewer batch entries than q is read periodically (entry b % n): Swin's shift mask
         p.mask_batch_period = mask.shape[0] if 1 < mask.shape[0] < batch else 0
 
@@ -122,12 +130,32 @@ def _check_inputs(q, k, v, q_bias, k_bias, mask):
         assert (mask.shape[0] in (1, batch) or batch % mask.shape[0] == 0) and mask.shape[1] in (1, nheads)
 
 
-def _workspace(nbytes: int, device) -> Optional[torch.Tensor]:
+def _raw_stream(device) -> int:
+    """cudaStream_t of torch's current stream on `device`, as an integer."""
+    return torch._C._cuda_getCurrentRawStream(device.index)
+
+
+class _on_device:
+    """`with` block that makes `device` current; does nothing when it already is (the usual case)."""
+
+    def __init__(self, device):
+        self.ctx = None if torch.cuda.current_device() == device.index else torch.cuda.device(device)
+
+    def __enter__(self):
+        if self.ctx is not None:
+            self.ctx.__enter__()
+
+    def __exit__(self, *exc):
+        if self.ctx is not None:
+            self.ctx.__exit__(*exc)
+
+
+def _workspace(nbytes: int, device, stream: int) -> Optional[torch.Tensor]:
     """Scratch for one call.  One buffer per (device, stream) is kept and grown on demand: calls on a stream
     are ordered, so the next call may overwrite it, and no allocation happens in the steady state."""
     if not nbytes:
         return None
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    key = (device.index, stream)
     ws = _ws_cache.get(key)
     if ws is None or ws.numel() < nbytes:
         ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
@@ -155,11 +183,12 @@ def flash_bias_forward(q, k, v, q_bias=None, k_bias=None, mask=None, causal=Fals
     _fill_common(p, q, k, v, q_bias, k_bias, mask, causal, float(softmax_scale), flags, alibi_slopes)
     p.o, p.o_stride = o.data_ptr(), _strides_bhs(o)
     p.lse, p.lse_stride_bh = lse.data_ptr(), seqlen_q_rounded
-    with torch.cuda.device(q.device):
-        ws = _workspace(lib.fb_fwd_workspace_bytes(C.byref(p)), q.device)
+    with _on_device(q.device):
+        stream = _raw_stream(q.device)
+        ws = _workspace(lib.fb_fwd_workspace_bytes(C.byref(p)), q.device, stream)
         if ws is not None:
             p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
-        _lib.check(lib.fb_fwd(C.byref(p), torch.cuda.current_stream().cuda_stream), "fb_fwd")
+        _lib.check(lib.fb_fwd(C.byref(p), stream), "fb_fwd")
     return o, lse, softmax_scale
 
 
@@ -194,11 +223,11 @@ def flash_bias_backward(do, q, k, v, o, q_bias, k_bias, lse, mask=None, causal=F
     if q_bias is not None:
         p.dq_bias, p.dk_bias = dq_bias.data_ptr(), dk_bias.data_ptr()
         p.dq_bias_stride, p.dk_bias_stride = _strides_bhs(dq_bias), _strides_bhs(dk_bias)
-    with torch.cuda.device(q.device):
-        ws = _workspace(lib.fb_bwd_workspace_bytes(C.byref(p)), q.device)
+    with _on_device(q.device):
+        stream = _raw_stream(q.device)
+        ws = _workspace(lib.fb_bwd_workspace_bytes(C.byref(p)), q.device, stream)
         if ws is not None:
             p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
-        stream = torch.cuda.current_stream().cuda_stream
         _lib.check(lib.fb_bwd_preprocess(C.byref(p), stream), "fb_bwd_preprocess")
         _lib.check(lib.fb_bwd(C.byref(p), stream), "fb_bwd")
     return dq, dk, dv, dq_bias, dk_bias
