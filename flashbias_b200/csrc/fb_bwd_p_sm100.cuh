@@ -5,8 +5,9 @@
 // the query-tile ring, the barrier phases, the P/dS buffers and the dQ accumulators run on counters that carry over
 // from item to item, so the loads of the next item's first query tiles are in flight while the last tiles of this
 // item are computed, and the allocation of tensor memory, the barrier set-up and the CTA launch happen once.
-// Between items the resident key tiles are reloaded once every product that reads them has completed, and the
-// dV / dK accumulators are handed over through one more barrier (acc_free).
+// Between items the resident key tiles are reloaded in two groups, each as soon as its last reader has completed
+// (the S|dP operands one query tile before the item ends), the dV / dK accumulators are handed over through one
+// more barrier (acc_free), and dV, dK and dk_bias leave as staged tiles through the copy engine.
 //
 // Short sequences are what this form is for (windowed attention: two query tiles per item), where the set-up
 // and drain of a CTA cost more than its tiles; with many query tiles per item the one-item-per-CTA kernel, whose
