@@ -70,8 +70,8 @@ CPU_SAMPLE = {
 # number of (batch, head, row) units - the tiles a CTA re-streams (Q, dO per key tile) are served by L2 at both
 # sizes, so DRAM traffic grows with the rows, not with the tile pairs
 NCU_BWD_TRAFFIC_BYTES = {
-    "alibi": (47.8e6 + 0.112e6) * (50 * 8192) / (16 * 4096),
-    "swin": (825.6e6 + 374.4e6) * 4096 / 256,
+    "alibi": (47.8e6 + 0.121e6) * (50 * 8192) / (16 * 4096),
+    "swin": (839.7e6 + 381.7e6) * 4096 / 256,
     "pde": 27.64e6 * (2 * 8 * 32768) / (4 * 8192),
 }
 
