@@ -226,13 +226,21 @@ bwd_t_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const uint32_t tq = tmem + Cfg::T_DQ + qb * D + lane_off;
         mbar_wait(dq_full + 8 * qb, (it / Cfg::NDQ) & 1, abort_flag, a.status);
         tc_fence_after_sync();
-        // the thread that issued the previous tile's reduction has seen its shared-memory reads complete
+        // The first columns are fetched into registers while the copy engine may still be reading the previous
+        // tile from the staging tile; the thread that issued that reduction then waits for its shared-memory
+        // reads and the warpgroup syncs.
+        uint32_t r0[16], r1[16];
+        tmem_ld16(tq, r0);
+        tmem_ld16(tq + 16, r1);
+        if (warp == 8 && lane == 0) bulk_wait_group_read0();
+        __syncwarp();
         asm volatile("bar.sync 3, 128;" ::: "memory");  // the drain warpgroup only
 #pragma unroll 1
         for (int c0 = 0; c0 < D; c0 += 32) {
-          uint32_t r0[16], r1[16];
-          tmem_ld16(tq + c0, r0);
-          tmem_ld16(tq + c0 + 16, r1);
+          if (c0 > 0) {
+            tmem_ld16(tq + c0, r0);
+            tmem_ld16(tq + c0 + 16, r1);
+          }
           tmem_wait_ld(r0);
           tmem_wait_ld(r1);
 #pragma unroll
@@ -249,9 +257,10 @@ bwd_t_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (warp == 8 && lane == 0) {
           bulk_reduce_add_f32(a.dq_acc + ((int64_t)bh * a.nq_tiles + (i_begin + it)) * (128 * D), sStg, 128 * D * 4);
           bulk_commit_group();
-          bulk_wait_group_read0();
         }
       }
+      // the staging tile must outlive the last reduction's reads; its global side completes with the kernel
+      if (warp == 8 && lane == 0) bulk_wait_group_read0();
     }
   } else if (n_it > 0) {
     // ------------------------------------------------------------------ compute warpgroups (warps 0-7)
