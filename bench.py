@@ -39,7 +39,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 from flashbias_b200.workloads import (alibi_slopes, flops_bwd, flops_fwd, make_device_workload,  # noqa: E402
-                                      make_workload)
+                                      make_workload, swin_shift_mask)
 
 FULL_SIZES = {
     "generic": dict(B=2, H=4, S=1024, D=32, R=8),
@@ -600,6 +600,24 @@ def main():
                 rec = sub_record(timer, o_fwd, o_step, off, ofb, bwd_bytes(osh, oqb.numel() + okb.numel()), peaks,
                                  max(3, n_sub // (4 if name in ("swin", "pde") else 1)))
                 others[name] = {**FULL_SIZES[name], "causal": ow.causal, **rec}
+                if name == "swin":
+                    # the same workload as a shifted-window block: additive 0 / -100 mask of 64 entries, read as
+                    # b % 64 by the kernels
+                    smask = swin_shift_mask(FULL_SIZES[name]["window"], 8).to(dev)
+
+                    def m_fwd():
+                        flash_bias_func(oq, ok_, ov, oqb, okb, smask, ow.causal, ow.softmax_scale)
+
+                    def m_step():
+                        for t in (oq, ok_, ov, oqb, okb):
+                            t.grad = None
+                        flash_bias_func(oq, ok_, ov, oqb, okb, smask, ow.causal, ow.softmax_scale).backward(ow.do)
+
+                    mbytes = bwd_bytes(osh, oqb.numel() + okb.numel()) + smask.numel() * 4
+                    rec = sub_record(timer, m_fwd, m_step, off, ofb, mbytes, peaks, max(3, n_sub // 4))
+                    others["swin_shifted"] = {**FULL_SIZES[name], "causal": ow.causal, "mask": "(64, 1, 256, 256) fp32",
+                                              **rec}
+                    del smask
                 del ow, oq, ok_, ov, oqb, okb
                 torch.cuda.empty_cache()
             line["detail"]["other_workloads"] = others

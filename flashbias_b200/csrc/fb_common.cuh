@@ -414,12 +414,31 @@ template <> __device__ __forceinline__ __half from_f32<__half>(float x) { return
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
 template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
 
+// 256-bit load through the read-only path (32-byte aligned address): one request covers a whole 32-byte sector.
+__device__ __forceinline__ void ldg_nc_v8(const void* p, uint32_t (&w)[8]) {
+  asm("ld.global.nc.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+               : "l"(p));
+}
+
 // 32 consecutive mask values of one row as fp32 (times log2 e).  `p` points at the first of them; `n` of them
 // exist (the rest read as 0); `vec` says that p is 16-byte aligned and n == 32.
 template <typename MT>
 __device__ __forceinline__ void load_mask_chunk(const MT* __restrict__ p, int n, bool vec, float (&mv)[32]) {
   constexpr float kLog2e = 1.4426950408889634f;
-  if (vec) {
+  if (vec && (reinterpret_cast<uintptr_t>(p) & 31) == 0) {
+    // Every thread reads its own row, so a load instruction of the warp touches 32 different lines whatever its
+    // width: 256-bit loads halve the number of instructions (and of line requests) of the 128-bit form.
+    constexpr int PER = 32 / (int)sizeof(MT);
+#pragma unroll
+    for (int g = 0; g < 32 / PER; ++g) {
+      uint32_t w[8];
+      ldg_nc_v8(reinterpret_cast<const char*>(p) + 32 * g, w);
+      const MT* e = reinterpret_cast<const MT*>(w);
+#pragma unroll
+      for (int i = 0; i < PER; ++i) mv[g * PER + i] = to_f32(e[i]) * kLog2e;
+    }
+  } else if (vec) {
     constexpr int PER = 16 / (int)sizeof(MT);
 #pragma unroll
     for (int g = 0; g < 32 / PER; ++g) {

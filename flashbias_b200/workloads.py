@@ -33,7 +33,7 @@ from typing import Optional
 import torch
 
 __all__ = ["Workload", "make_workload", "make_device_workload", "WORKLOADS", "flops_fwd", "flops_bwd",
-           "attended_pairs"]
+           "attended_pairs", "alibi_slopes", "swin_shift_mask"]
 
 
 @dataclass
@@ -128,6 +128,22 @@ def _swin_table(window: int, H: int, hidden: int = 512) -> torch.Tensor:
     dx = xs[:, None] - xs[None, :] + window - 1
     idx = dy * (2 * window - 1) + dx
     return feat[idx.reshape(-1)].reshape(window * window, window * window, H).permute(2, 0, 1).contiguous()
+
+
+def swin_shift_mask(window: int = 16, grid: int = 8) -> torch.Tensor:
+    """(grid*grid, 1, N, N) fp32 additive mask of a shifted-window block, N = window*window: 0 where two tokens
+    of a window come from the same image region, -100 elsewhere (the reference's call site builds it from the
+    region map of the cyclically shifted image, 2_Vision_Transformer/swin_transformer_v2.py:189-192, :260-283).
+    With a shift of half a window only the windows of the last row and column of the window grid straddle
+    regions; the mask of batch entry b is entry b % (grid*grid)."""
+    shift = window // 2
+    ys, xs = torch.meshgrid(torch.arange(window), torch.arange(window), indexing="ij")
+    out = torch.zeros(grid * grid, 1, window * window, window * window)
+    for wy in range(grid):
+        for wx in range(grid):
+            region = (2 * ((ys >= window - shift) & (wy == grid - 1)) + ((xs >= window - shift) & (wx == grid - 1))).flatten()
+            out[wy * grid + wx, 0] = torch.where(region[:, None] == region[None, :], 0.0, -100.0)
+    return out
 
 
 def _swin_factors(B=4096, H=24, window=16, D=32, R=16, **_):

@@ -8,7 +8,7 @@ import pytest
 import torch
 
 from flashbias_b200 import flash_bias_func
-from flashbias_b200.workloads import make_workload
+from flashbias_b200.workloads import make_workload, swin_shift_mask
 from oracle import flashbias_oracle as orc
 from tests.helpers import check_close
 
@@ -76,6 +76,30 @@ def test_full_size_slices_match_checker(name):
                 err_fp32 = (g_ref[idx].double() - truth).abs().max().item()
                 bound = 4.0 * err_fp32 + 2e-2 * max(1.0, truth.abs().max().item())
                 assert err_kernel <= bound, f"{name}[{b},{h}]/{key}: {err_kernel:.3e} > {bound:.3e} (fp32 checker {err_fp32:.3e})"
+
+
+def test_full_size_swin_with_shift_mask():
+    """The windowed workload at full size with the shifted-window mask (64 mask entries read as b % 64, never
+    expanded to the 4096 windows): slices with and without masked regions against the checker."""
+    sizes = dict(B=4096, H=24, window=16, D=32, R=16)
+    w = make_workload("swin", **sizes)
+    mask = swin_shift_mask(16, 8)
+    d = w.to("cuda")
+    q, k, v, qb, kb = (t.requires_grad_(True) for t in (d.q, d.k, d.v, d.q_bias, d.k_bias))
+    o = flash_bias_func(q, k, v, qb, kb, mask.cuda(), False, w.softmax_scale)
+    o.backward(d.do)
+    torch.cuda.synchronize()
+    assert torch.isfinite(o).all()
+    for (b, h) in [(0, 0), (63, 5), (4039, 17), (4095, 23)]:   # windows 0 (no regions), 63, 7 (two regions), 63 (four)
+        ins = [_slice(t, b, h) for t in (w.q, w.k, w.v, w.q_bias, w.k_bias)]
+        m = mask[b % 64:b % 64 + 1]
+        o_ref, lse_ref = orc.attention_forward(*ins, m, False, w.softmax_scale)
+        o_got = o[b:b + 1, :, h:h + 1].detach().float().cpu()
+        check_close(f"swin_shifted[{b},{h}]/o", o_got, o_ref, w.dtype)
+        g_ref = orc.attention_backward(_slice(w.do, b, h), ins[0], ins[1], ins[2], o_got, lse_ref, ins[3], ins[4], m,
+                                       False, w.softmax_scale)
+        for key, t, ref in zip(("dq", "dk", "dv"), (q, k, v), g_ref[:3]):
+            check_close(f"swin_shifted[{b},{h}]/{key}", t.grad[b:b + 1, :, h:h + 1], ref, w.dtype)
 
 
 def test_full_size_softmax_rows_sum_to_one():
