@@ -179,10 +179,10 @@ int fb_prepare_rows(const void *x, int32_t x_dtype, const int64_t *x_stride, voi
  * The first call on each device looks up the device address of the array (cudaGetSymbolAddress, with
  * that device current), and the first call of each kernel variant on a device raises that kernel's
  * shared-memory limit (and, under lazy module loading, loads its code); make one warm-up call per device
- * and problem kind outside any stream capture and outside the hook that forbids allocation.  All calls on a device share
- * the one array, which keeps the previous call's contents: every byte a call reads it has written
- * itself first, so nothing needs clearing, but two calls that overlap on the GPU (different streams)
- * race on it -- keep them on one stream or order them with events.
+ * and problem kind outside any stream capture and outside the hook that forbids allocation.  All
+ * calls on a device share the one array, which keeps the previous call's contents: every byte a call
+ * reads it has written itself first, so nothing needs clearing, but two calls that overlap on the GPU
+ * (different streams) race on it -- keep them on one stream or order them with events.
  */
 #define FB_NOALLOC_SCRATCH_BYTES (32u << 20)
 size_t fb_fwd_noalloc_capacity(void);
