@@ -891,9 +891,6 @@ int bwd_prepare(const fb_params* p, const PackPlan& plan, cudaStream_t st, BwdLa
   void* qpack = ws + w.off_qpack;
   void* kpack = ws + w.off_kpack;
   void* kcenter = ws + w.off_kcenter;
-  if ((rc = launch_pack_operands(p, plan, qpack, kpack, kcenter, true, ws + w.off_qs, st))) return rc;
-  cudaError_t e = cudaMemsetAsync(ws + w.off_dq, 0, w.zero_bytes, st);
-  if (e != cudaSuccess) return (int)e;
   CUtensorMap &tQ = L.tQ, &tK = L.tK, &tV = L.tV, &tDO = L.tDO, &tQb = L.tQb, &tKb = L.tKb, &tKc = L.tKc, &tKs = L.tKs;
   if ((rc = make_tmap_4d(&tQ, p->q, D, p->Sq, p->H, p->B, p->q_stride[2], p->q_stride[1], p->q_stride[0], D, 128)))
     return rc;
@@ -966,6 +963,10 @@ int bwd_prepare(const fb_params* p, const PackPlan& plan, cudaStream_t st, BwdLa
   a.mask_dtype = p->mask_dtype;
   a.mask_batch_period = p->mask_batch_period;
   a.alibi_slopes = p->alibi_slopes;
+  // launches last: the tensor maps and arguments above are ready when the main kernel's turn comes
+  if ((rc = launch_pack_operands(p, plan, qpack, kpack, kcenter, true, ws + w.off_qs, st))) return rc;
+  cudaError_t e = cudaMemsetAsync(ws + w.off_dq, 0, w.zero_bytes, st);
+  if (e != cudaSuccess) return (int)e;
   return 0;
 }
 

@@ -486,7 +486,6 @@ int launch_fwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
     void* qpack = ws;
     void* kpack = ws + plan.q_bytes;
     void* qs = ws + plan.q_bytes + plan.k_bytes;
-    if ((rc = launch_pack_operands(p, plan, qpack, kpack, nullptr, false, qs, st))) return rc;
     CUtensorMap tQ, tK, tV, tQb, tKb;
     constexpr int BOXD = D > 64 ? 64 : D;
     constexpr int BOXR = RP > 64 ? 64 : (RP ? RP : 16);
@@ -537,6 +536,9 @@ int launch_fwd_t(const fb_params* p, const PackPlan& plan, cudaStream_t st) {
     a.mask_dtype = p->mask_dtype;
     a.mask_batch_period = p->mask_batch_period;
     a.alibi_slopes = p->alibi_slopes;
+    // (the tensor maps above are encoded first: the host then has the main kernel's launch ready while the operand
+    // preparation runs)
+    if ((rc = launch_pack_operands(p, plan, qpack, kpack, nullptr, false, qs, st))) return rc;
     auto kern = fwd_sm100_kernel<T, D, RP, NQ, ALIBI>;
     // per kernel instantiation and device: raise the dynamic shared-memory limit once
     static std::mutex mu;
