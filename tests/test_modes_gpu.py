@@ -246,7 +246,8 @@ BWD_FORM_CASES = [
     (2, 40, 1024, 1024, 2, True, None, False, torch.bfloat16),    # causal: items of 8 ... 1 query tiles
     (3, 50, 200, 1000, 8, True, 0.25, False, torch.float16),      # causal, Sq < Sk: key tiles no query sees; scale 2^-2
     (5, 31, 130, 257, 24, False, 1.0, False, torch.float16),      # ragged tiles, packed rank 32, scale 1
-    (1, 3, 384, 384, 40, False, None, False, torch.bfloat16),     # fewer items than SMs, packed rank 64
+    (1, 3, 384, 384, 28, False, None, False, torch.bfloat16),     # fewer items than SMs, packed rank 64
+    (2, 37, 640, 512, 12, True, 0.125, False, torch.bfloat16),    # causal, Sq > Sk, bf16 with a power-of-two scale
 ]
 
 
