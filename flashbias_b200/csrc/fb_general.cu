@@ -333,22 +333,34 @@ __global__ void __launch_bounds__(kWarps * 32) bwd_dkv_general_kernel(const fb_p
 // rows are consecutive floats, which keeps the threads' shared-memory stores free of bank conflicts); `slots`
 // copies at distance `slot_stride` are summed.
 template <typename T>
-__global__ void factor_grad_store_kernel(const float* __restrict__ acc, int64_t ab, int64_t ah, int64_t as, int tiled,
-                                         int slots, int64_t slot_stride,
-                                         T* __restrict__ out, int Bx, int S, int Hx, int R, int64_t sb, int64_t sh,
-                                         int64_t ss) {
-  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int64_t total = (int64_t)Bx * S * Hx * R;
+struct FactorStoreJob {
+  const float* acc;
+  int64_t ab, ah, as;
+  int tiled, slots;
+  int64_t slot_stride;
+  T* out;
+  int Bx, S, Hx;
+  int64_t sb, sh, ss;
+};
+
+// One launch for both factors: blocks [0, nbq) store dq_bias, the rest dk_bias.
+template <typename T>
+__global__ void __launch_bounds__(256) factor_grad_store_kernel(FactorStoreJob<T> jq, FactorStoreJob<T> jk, unsigned nbq,
+                                                                int R) {
+  const bool is_q = blockIdx.x < nbq;
+  const FactorStoreJob<T>& j = is_q ? jq : jk;
+  const int64_t idx = (int64_t)(is_q ? blockIdx.x : blockIdx.x - nbq) * blockDim.x + threadIdx.x;
+  const int64_t total = (int64_t)j.Bx * j.S * j.Hx * R;
   if (idx >= total) return;
   const int r = (int)(idx % R);
-  const int h = (int)((idx / R) % Hx);
-  const int s = (int)((idx / ((int64_t)R * Hx)) % S);
-  const int b = (int)(idx / ((int64_t)R * Hx * S));
-  const float* src = tiled ? acc + b * ab + h * ah + (int64_t)(s / 128) * (128 * R) + r * 128 + (s % 128)
-                           : acc + b * ab + h * ah + s * as + r;
+  const int h = (int)((idx / R) % j.Hx);
+  const int s = (int)((idx / ((int64_t)R * j.Hx)) % j.S);
+  const int b = (int)(idx / ((int64_t)R * j.Hx * j.S));
+  const float* src = j.tiled ? j.acc + b * j.ab + h * j.ah + (int64_t)(s / 128) * (128 * R) + r * 128 + (s % 128)
+                             : j.acc + b * j.ab + h * j.ah + s * j.as + r;
   float v = 0.f;
-  for (int e = 0; e < slots; ++e) v += src[e * slot_stride];
-  out[b * sb + h * sh + s * ss + r] = from_f32<T>(v);
+  for (int e = 0; e < j.slots; ++e) v += src[e * j.slot_stride];
+  j.out[b * j.sb + h * j.sh + s * j.ss + r] = from_f32<T>(v);
 }
 
 size_t bwd_general_workspace(const fb_params* p) {
@@ -360,27 +372,26 @@ size_t bwd_general_workspace(const fb_params* p) {
 }
 
 template <typename T>
-static void launch_one_factor_store(const float* acc, FactorAccLayout l, T* out, int Bx, int S, int Hx, int R,
-                                    const int64_t* stride, cudaStream_t st) {
-  const int64_t n = (int64_t)Bx * S * Hx * R;
-  const unsigned blocks = (unsigned)((n + 255) / 256);
+static FactorStoreJob<T> factor_store_job(const float* acc, FactorAccLayout l, T* out, int Bx, int S, int Hx, int R,
+                                          const int64_t* stride) {
   if (l.rows > 0)  // (slots, Bx, Hx, rows, R)
-    factor_grad_store_kernel<T><<<blocks, 256, 0, st>>>(acc, Hx * l.rows * R, l.rows * R, R, 1, l.slots, l.slot_stride,
-                                                        out, Bx, S, Hx, R, stride[0], stride[1], stride[2]);
-  else  // (Bx, S, Hx, R)
-    factor_grad_store_kernel<T><<<blocks, 256, 0, st>>>(acc, (int64_t)S * Hx * R, R, (int64_t)Hx * R, 0, 1, 0, out, Bx,
-                                                        S, Hx, R, stride[0], stride[1], stride[2]);
+    return {acc, Hx * l.rows * R, l.rows * R, R, 1, l.slots, l.slot_stride, out, Bx, S, Hx, stride[0], stride[1], stride[2]};
+  // (Bx, S, Hx, R)
+  return {acc, (int64_t)S * Hx * R, R, (int64_t)Hx * R, 0, 1, 0, out, Bx, S, Hx, stride[0], stride[1], stride[2]};
 }
 
 template <typename T>
 static int launch_store_factor_grads(const fb_params* p, float* dqb, float* dkb, cudaStream_t st,
                                      FactorAccLayout ql, FactorAccLayout kl) {
   const FactorAcc fa = factor_acc(*p);
-  launch_one_factor_store<T>(dqb, ql, reinterpret_cast<T*>(p->dq_bias), fa.Bq, p->Sq, fa.Hq, p->R,
-                             p->dq_bias_stride, st);
-  launch_one_factor_store<T>(dkb, kl, reinterpret_cast<T*>(p->dk_bias), fa.Bk, p->Sk, fa.Hk, p->R,
-                             p->dk_bias_stride, st);
-  note_launch(2);
+  const FactorStoreJob<T> jq = factor_store_job<T>(dqb, ql, reinterpret_cast<T*>(p->dq_bias), fa.Bq, p->Sq, fa.Hq, p->R,
+                                                   p->dq_bias_stride);
+  const FactorStoreJob<T> jk = factor_store_job<T>(dkb, kl, reinterpret_cast<T*>(p->dk_bias), fa.Bk, p->Sk, fa.Hk, p->R,
+                                                   p->dk_bias_stride);
+  const unsigned nbq = (unsigned)(((int64_t)fa.Bq * p->Sq * fa.Hq * p->R + 255) / 256);
+  const unsigned nbk = (unsigned)(((int64_t)fa.Bk * p->Sk * fa.Hk * p->R + 255) / 256);
+  factor_grad_store_kernel<T><<<nbq + nbk, 256, 0, st>>>(jq, jk, nbq, p->R);
+  note_launch();
   return (int)cudaGetLastError();
 }
 
